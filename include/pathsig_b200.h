@@ -1,0 +1,134 @@
+/*
+ * pathsig_b200 — C ABI of the B200 (sm_100a) signature / log-signature library.
+ *
+ * Plain pointers and sizes only: no C++ types, no torch types, no exceptions.  Every entry
+ * point enqueues work on the given CUDA stream of the CURRENT device and returns without
+ * synchronising.  Unless an entry point's comment says otherwise, nothing here allocates
+ * device memory: outputs and scratch are supplied by the caller.  Return value: PSIG_OK (0)
+ * or a negative PsigStatus; psig_status_string() gives the text.
+ *
+ * Each entry point replaces one operator of the reference (paths below are relative to the
+ * reference project root):
+ *   psig_sig_forward      <- pathsig::compute_signature   (src/pathsig/bindings.cpp:9-20,
+ *                            launcher src/pathsig/forward/sig_launch.cu:75-225)
+ *   psig_sig_backward     <- pathsig::signature_backward  (src/pathsig/bindings.cpp:23-36,
+ *                            launcher src/pathsig/backward/sig_backward_launch.cu:83-303)
+ *   psig_logsig_forward   <- pathsig::sig_to_logsig       (src/pathsig/bindings.cpp:39-49,
+ *                            launcher src/pathsig/forward/sig_launch.cu:230-339)
+ *   psig_logsig_backward  <- pathsig::logsig_backward     (src/pathsig/bindings.cpp:52-63,
+ *                            launcher src/pathsig/backward/sig_backward_launch.cu:307-460)
+ *
+ * Data conventions (identical to the reference operators):
+ *   path        (B, L, d) contiguous, float32 or float64, L >= 2
+ *   windows     (W, 2) contiguous int32, half-open point ranges [start, end); a window with
+ *               end - start < 2 yields zeros.  W == 0 / NULL: one unit per path, the whole path.
+ *   signature   (B, D) or (B, W, D); degrees 1..depth concatenated; a dense degree k has d^k
+ *               entries in lexicographic order, a projected degree keeps the caller's order.
+ *   words       base-d codes (first letter most significant) of the NON-complete degrees,
+ *               concatenated by degree, int64, device memory.
+ *   level_sizes level_sizes[k] = number of words kept at degree k (entry 0 unused).  Ignored
+ *               when `projected` is 0 (all degrees dense).
+ */
+#ifndef PATHSIG_B200_H
+#define PATHSIG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PSIG_MAX_DEPTH 12
+#define PSIG_ABI_VERSION 1
+
+typedef enum PsigStatus {
+    PSIG_OK = 0,
+    PSIG_ERR_NULL = -1,        /* a required pointer is NULL */
+    PSIG_ERR_DTYPE = -2,       /* dtype is neither PSIG_F32 nor PSIG_F64 */
+    PSIG_ERR_DEPTH = -3,       /* depth outside 1..12 */
+    PSIG_ERR_SHAPE = -4,       /* B < 0, L < 2, d < 1, W < 0 or inconsistent level_sizes */
+    PSIG_ERR_PACKING = -5,     /* d needs more than 64/depth bits per letter */
+    PSIG_ERR_WORKSPACE = -6,   /* workspace too small or NULL */
+    PSIG_ERR_CUDA = -7,        /* a CUDA runtime call or launch failed (see cudaGetLastError) */
+    PSIG_ERR_TOO_LARGE = -8,   /* a size exceeds what the entry point supports */
+    PSIG_ERR_UNSUPPORTED = -9  /* configuration has no kernel */
+} PsigStatus;
+
+typedef enum PsigDtype { PSIG_F32 = 0, PSIG_F64 = 1 } PsigDtype;
+
+/* Algorithm selection for psig_sig_forward / psig_sig_backward (desc.algo). */
+typedef enum PsigAlgo {
+    PSIG_ALGO_AUTO = 0,    /* register-tiled kernel when one exists for (dtype, d, depth), else generic */
+    PSIG_ALGO_GENERIC = 1, /* always the generic per-prefix kernel */
+    PSIG_ALGO_TILED = 2    /* register-tiled kernel or PSIG_ERR_UNSUPPORTED */
+} PsigAlgo;
+
+/* Problem description shared by the signature entry points. */
+typedef struct PsigSigDesc {
+    int32_t dtype;                            /* PsigDtype */
+    int32_t d;                                /* channels */
+    int32_t depth;                            /* truncation depth, 1..12 */
+    int32_t projected;                        /* 0: all degrees dense; 1: level_sizes / words in force */
+    int64_t B;                                /* paths */
+    int64_t L;                                /* points per path */
+    int64_t W;                                /* windows; 0 = none */
+    const int32_t *windows;                   /* device (W, 2) or NULL */
+    const int64_t *words;                     /* device codes of non-complete degrees, or NULL */
+    int64_t level_sizes[PSIG_MAX_DEPTH + 1];  /* host */
+    int32_t algo;                             /* PsigAlgo */
+    int32_t reserved;
+} PsigSigDesc;
+
+/* Problem description of the signature <-> log-signature entry points.  The signature is in
+ * the hybrid layout: degrees below `depth` dense, the top degree dense (top_size == d^depth,
+ * top_words NULL) or an explicit list of top_size words. */
+typedef struct PsigLogDesc {
+    int32_t dtype;
+    int32_t d;
+    int32_t depth;
+    int32_t reserved;
+    int64_t rows;               /* B or B*W */
+    int64_t top_size;           /* words kept at degree `depth` */
+    const int64_t *top_words;   /* device codes of the top degree, or NULL when it is dense */
+} PsigLogDesc;
+
+int psig_abi_version(void);
+const char *psig_status_string(int status);
+
+/* Width D of one signature row for this description, or a negative PsigStatus. */
+int64_t psig_sig_size(const PsigSigDesc *desc);
+/* Width of one row in the hybrid layout of a PsigLogDesc, or a negative PsigStatus. */
+int64_t psig_logsig_size(const PsigLogDesc *desc);
+
+/* out[(b*max(W,1)+w)*D + i] = signature coordinate i of path b over window w.
+ * Replaces pathsig::compute_signature (src/pathsig/forward/sig_launch.cu:75-225). */
+int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void *stream);
+
+/* Scratch bytes psig_sig_backward needs for this description (may be 0). */
+int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
+
+/* grad_path (B, L, d) = d/dpath of sum(signature * grad_sig).  `sig` is the forward output for
+ * the same description.  Contributions of overlapping windows are summed.  `workspace` must hold
+ * psig_sig_backward_workspace(desc) bytes, 256-byte aligned; its contents are overwritten.
+ * Replaces pathsig::signature_backward (src/pathsig/backward/sig_backward_launch.cu:83-303). */
+int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
+                      void *grad_path, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* logsig (rows, S) = word coordinates of the truncated tensor logarithm of `sig` (rows, S);
+ * cache (rows, S*depth) receives the intermediate powers that psig_logsig_backward reads.
+ * Replaces pathsig::sig_to_logsig (src/pathsig/forward/sig_launch.cu:230-339). */
+int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, void *cache, void *stream);
+
+/* Scratch bytes psig_logsig_backward needs (rows * S * depth scalars). */
+int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
+
+/* grad_sig (rows, S) = adjoint of psig_logsig_forward applied to grad_logsig.
+ * Replaces pathsig::logsig_backward (src/pathsig/backward/sig_backward_launch.cu:307-460). */
+int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,
+                         void *grad_sig, void *workspace, int64_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PATHSIG_B200_H */

@@ -1,0 +1,90 @@
+"""Compile the reference's own CUDA operators, unchanged, into ``oracle/_ref/libpathsig_ops.so``.
+
+TEST INFRASTRUCTURE ONLY.  The reference has no CPU implementation, so its CUDA build is the
+strongest parity pin there is: the GPU tests load this library next to ours (its operators
+live in ``torch.ops.pathsig``, ours in ``torch.ops.pathsig_b200``) and compare outputs on the
+same tensors, and ``tests/golden/make_golden.py`` records its outputs as fixtures.
+
+The sources are compiled where they lie (``$PATHSIG_REFERENCE_ROOT``, default
+``/root/reference``) with plain nvcc commands; the reference's own CMake build is not run and
+no source file is copied.  Outputs go to ``oracle/_ref/`` only, which git ignores.  When the
+reference tree is absent (for example on a GPU box) the function leaves an existing library
+alone and reports whether one is there.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT_DIR = os.path.join(HERE, "_ref")
+LIB = os.path.join(OUT_DIR, "libpathsig_ops.so")
+SOURCES = [
+    "src/pathsig/bindings.cpp",
+    "src/pathsig/forward/sig_launch.cu",
+    "src/pathsig/forward/sig_kernels.cu",
+    "src/pathsig/backward/sig_backward_launch.cu",
+    "src/pathsig/backward/sig_backward_kernels.cu",
+]
+
+
+def reference_root() -> str:
+    return os.environ.get("PATHSIG_REFERENCE_ROOT", "/root/reference")
+
+
+def build(force: bool = False, verbose: bool = False) -> bool:
+    """Returns True when ``oracle/_ref/libpathsig_ops.so`` exists afterwards."""
+    root = reference_root()
+    srcs = [os.path.join(root, s) for s in SOURCES]
+    if not all(os.path.isfile(s) for s in srcs):
+        return os.path.isfile(LIB)
+    if os.path.isfile(LIB) and not force:
+        newest = max(os.path.getmtime(s) for s in srcs)
+        if os.path.getmtime(LIB) >= newest:
+            return True
+
+    import torch
+    from torch.utils import cpp_extension
+
+    os.makedirs(OUT_DIR, exist_ok=True)
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    includes = [os.path.join(root, "src", "pathsig")] + cpp_extension.include_paths("cuda")
+    flags = [
+        "-gencode", "arch=compute_100,code=sm_100", "-ccbin", "/usr/bin/g++", "-std=c++17", "-O3", "-DNDEBUG",
+        "-rdc=true", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+        f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+    ]
+    for inc in includes:
+        flags += ["-isystem" if "torch" in inc else "-I", inc]
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(OUT_DIR, os.path.basename(src).rsplit(".", 1)[0] + ".o")
+        cmd = [nvcc] + flags + ["-x", "cu", "-c", src, "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"reference build failed for {src}:\n{res.stderr[-4000:]}")
+        if verbose:
+            print("compiled", src, file=sys.stderr)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(srcs)) as pool:
+        objs = list(pool.map(compile_one, srcs))
+
+    lib_dirs = cpp_extension.library_paths("cuda")
+    link = [nvcc, "-gencode", "arch=compute_100,code=sm_100", "-ccbin", "/usr/bin/g++", "-shared", "-o", LIB] + objs
+    for ld in lib_dirs:
+        link += ["-L", ld, "-Xlinker", f"-rpath={ld}"]
+    link += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
+    res = subprocess.run(link, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"reference link failed:\n{res.stderr[-4000:]}")
+    for o in objs:
+        os.remove(o)
+    return True
+
+
+if __name__ == "__main__":
+    ok = build(force="--force" in sys.argv, verbose=True)
+    print("reference library:", LIB if ok else "unavailable")

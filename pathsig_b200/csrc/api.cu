@@ -1,0 +1,225 @@
+// C ABI of libpathsig_b200.so: argument checks, level bookkeeping and kernel selection.
+// Declarations and the reference operators they stand in for: include/pathsig_b200.h.
+#include "common.cuh"
+
+namespace psig {
+
+int make_level_table(int d, int depth, bool projected, const int64_t *level_sizes, const int64_t *words,
+                     bool top_only, LevelTable *out)
+{
+    LevelTable &lt = *out;
+    lt.d = d;
+    lt.depth = depth;
+    long long d_pow = 1, off = 0, dense_off = 0, used = 0;
+    bool all_dense = true;
+    for (int k = 0; k <= kMaxDepth; ++k) {
+        lt.size[k] = 0; lt.offset[k] = 0; lt.words[k] = nullptr; lt.dense_offset[k] = 0; lt.lower_dense[k] = true;
+    }
+    for (int k = 1; k <= depth; ++k) {
+        if (d_pow > (long long)(0x7fffffffffffffffLL / d)) return PSIG_ERR_PACKING;
+        d_pow *= d;
+        long long size = d_pow;
+        const long long *w = nullptr;
+        if (projected && (!top_only || k == depth)) {
+            size = level_sizes[k];
+            if (size < 0) return PSIG_ERR_SHAPE;
+            if (size != d_pow) {
+                if (size > 0 && !words) return PSIG_ERR_NULL;
+                w = reinterpret_cast<const long long *>(words) + used;
+                used += size;
+            }
+        }
+        lt.size[k] = size;
+        lt.offset[k] = off;
+        lt.words[k] = w;
+        lt.dense_offset[k] = dense_off;
+        lt.lower_dense[k] = all_dense;
+        if (w != nullptr || size != d_pow) all_dense = false;
+        off += size;
+        dense_off += d_pow;
+    }
+    lt.total = off;
+    return PSIG_OK;
+}
+
+namespace {
+
+int check_sig_desc(const PsigSigDesc *desc)
+{
+    if (!desc) return PSIG_ERR_NULL;
+    if (desc->dtype != PSIG_F32 && desc->dtype != PSIG_F64) return PSIG_ERR_DTYPE;
+    if (desc->depth < 1 || desc->depth > kMaxDepth) return PSIG_ERR_DEPTH;
+    if (desc->B < 0 || desc->L < 2 || desc->d < 1 || desc->W < 0) return PSIG_ERR_SHAPE;
+    if (desc->W > 0 && !desc->windows) return PSIG_ERR_NULL;
+    return PSIG_OK;
+}
+
+int sig_table(const PsigSigDesc *desc, LevelTable *lt)
+{
+    const int rc = check_sig_desc(desc);
+    if (rc != PSIG_OK) return rc;
+    return make_level_table(desc->d, desc->depth, desc->projected != 0, desc->level_sizes, desc->words, false, lt);
+}
+
+int log_table(const PsigLogDesc *desc, LevelTable *lt)
+{
+    if (!desc) return PSIG_ERR_NULL;
+    if (desc->dtype != PSIG_F32 && desc->dtype != PSIG_F64) return PSIG_ERR_DTYPE;
+    if (desc->depth < 1 || desc->depth > kMaxDepth) return PSIG_ERR_DEPTH;
+    if (desc->rows < 0 || desc->d < 1 || desc->top_size < 0) return PSIG_ERR_SHAPE;
+    int64_t sizes[kMaxDepth + 1] = {0};
+    sizes[desc->depth] = desc->top_size;
+    return make_level_table(desc->d, desc->depth, true, sizes, desc->top_words, true, lt);
+}
+
+bool use_tiled(const PsigSigDesc *desc, int *rc)
+{
+    *rc = PSIG_OK;
+    const bool eligible = desc->dtype == PSIG_F32 && !desc->projected && tiled_supported(desc->d, desc->depth);
+    if (desc->algo == PSIG_ALGO_GENERIC) return false;
+    if (desc->algo == PSIG_ALGO_TILED && !eligible) { *rc = PSIG_ERR_UNSUPPORTED; return false; }
+    return eligible;
+}
+
+size_t dtype_size(int dtype) { return dtype == PSIG_F32 ? 4 : 8; }
+
+}  // namespace
+}  // namespace psig
+
+using namespace psig;
+
+extern "C" {
+
+int psig_abi_version(void) { return PSIG_ABI_VERSION; }
+
+const char *psig_status_string(int status)
+{
+    switch (status) {
+        case PSIG_OK: return "ok";
+        case PSIG_ERR_NULL: return "a required pointer is NULL";
+        case PSIG_ERR_DTYPE: return "dtype must be float32 or float64";
+        case PSIG_ERR_DEPTH: return "depth must be in [1,12]";
+        case PSIG_ERR_SHAPE: return "invalid shape (need B >= 0, L >= 2, d >= 1, W >= 0, consistent level sizes)";
+        case PSIG_ERR_PACKING: return "d^depth does not fit a 64-bit word code";
+        case PSIG_ERR_WORKSPACE: return "workspace missing or too small";
+        case PSIG_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+        case PSIG_ERR_TOO_LARGE: return "problem size exceeds what this entry point supports";
+        case PSIG_ERR_UNSUPPORTED: return "no kernel for this configuration";
+        default: return "unknown status";
+    }
+}
+
+int64_t psig_sig_size(const PsigSigDesc *desc)
+{
+    LevelTable lt;
+    const int rc = sig_table(desc, &lt);
+    return rc != PSIG_OK ? rc : lt.total;
+}
+
+int64_t psig_logsig_size(const PsigLogDesc *desc)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    return rc != PSIG_OK ? rc : lt.total;
+}
+
+int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void *stream)
+{
+    LevelTable lt;
+    int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->B == 0 || lt.total == 0) return PSIG_OK;
+    if (!path || !out) return PSIG_ERR_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tiled = use_tiled(desc, &rc);
+    if (rc != PSIG_OK) return rc;
+    if (tiled) return tiled_sig_forward(*desc, static_cast<const float *>(path), static_cast<float *>(out), st);
+    if (desc->dtype == PSIG_F32)
+        return generic_sig_forward<float>(*desc, lt, static_cast<const float *>(path), static_cast<float *>(out), st);
+    return generic_sig_forward<double>(*desc, lt, static_cast<const double *>(path), static_cast<double *>(out), st);
+}
+
+int64_t psig_sig_backward_workspace(const PsigSigDesc *desc)
+{
+    LevelTable lt;
+    int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    const bool tiled = use_tiled(desc, &rc);
+    if (rc != PSIG_OK) return rc;
+    if (tiled) return tiled_sig_backward_workspace(*desc);
+    return (int64_t)dtype_size(desc->dtype) * desc->B * (desc->L - 1) * desc->d;
+}
+
+int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
+                      void *grad_path, void *workspace, int64_t workspace_bytes, void *stream)
+{
+    LevelTable lt;
+    int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->B == 0) return PSIG_OK;
+    if (!path || !grad_path) return PSIG_ERR_NULL;
+    if (lt.total > 0 && (!sig || !grad_sig)) return PSIG_ERR_NULL;
+    const int64_t need = psig_sig_backward_workspace(desc);
+    if (need < 0) return (int)need;
+    if (need > 0 && (!workspace || workspace_bytes < need)) return PSIG_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tiled = use_tiled(desc, &rc);
+    if (rc != PSIG_OK) return rc;
+    if (tiled)
+        return tiled_sig_backward(*desc, static_cast<const float *>(path), static_cast<const float *>(sig),
+                                  static_cast<const float *>(grad_sig), static_cast<float *>(grad_path), workspace, st);
+    if (desc->dtype == PSIG_F32)
+        return generic_sig_backward<float>(*desc, lt, static_cast<const float *>(path),
+                                           static_cast<const float *>(sig), static_cast<const float *>(grad_sig),
+                                           static_cast<float *>(grad_path), static_cast<float *>(workspace), st);
+    return generic_sig_backward<double>(*desc, lt, static_cast<const double *>(path),
+                                        static_cast<const double *>(sig), static_cast<const double *>(grad_sig),
+                                        static_cast<double *>(grad_path), static_cast<double *>(workspace), st);
+}
+
+int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, void *cache, void *stream)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
+    if (!sig || !logsig || !cache) return PSIG_ERR_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == PSIG_F32)
+        return generic_logsig_forward<float>(*desc, lt, static_cast<const float *>(sig), static_cast<float *>(logsig),
+                                             static_cast<float *>(cache), st);
+    return generic_logsig_forward<double>(*desc, lt, static_cast<const double *>(sig), static_cast<double *>(logsig),
+                                          static_cast<double *>(cache), st);
+}
+
+int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    return (int64_t)dtype_size(desc->dtype) * desc->rows * lt.total * desc->depth;
+}
+
+int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,
+                         void *grad_sig, void *workspace, int64_t workspace_bytes, void *stream)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
+    if (!sig || !cache || !grad_logsig || !grad_sig) return PSIG_ERR_NULL;
+    const int64_t need = psig_logsig_backward_workspace(desc);
+    if (!workspace || workspace_bytes < need) return PSIG_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == PSIG_F32)
+        return generic_logsig_backward<float>(*desc, lt, static_cast<const float *>(sig),
+                                              static_cast<const float *>(cache),
+                                              static_cast<const float *>(grad_logsig), static_cast<float *>(grad_sig),
+                                              static_cast<float *>(workspace), st);
+    return generic_logsig_backward<double>(*desc, lt, static_cast<const double *>(sig),
+                                           static_cast<const double *>(cache),
+                                           static_cast<const double *>(grad_logsig), static_cast<double *>(grad_sig),
+                                           static_cast<double *>(workspace), st);
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+// Shared declarations of the pathsig_b200 CUDA library (internal header).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pathsig_b200.h"
+
+namespace psig {
+
+constexpr int kMaxDepth = PSIG_MAX_DEPTH;
+
+// One row of the signature as the kernels see it: per degree the number of kept words, where
+// the degree starts inside the row, and the explicit codes (nullptr = dense degree).
+// Mirrors the bookkeeping of the reference launchers (src/pathsig/forward/sig_launch.cu:167-182).
+struct LevelTable {
+    int d;
+    int depth;
+    long long size[kMaxDepth + 1];
+    long long offset[kMaxDepth + 1];
+    const long long *words[kMaxDepth + 1];
+    long long total;        // row width D
+    long long dense_offset[kMaxDepth + 1];  // start of degree k in a fully dense row
+    bool lower_dense[kMaxDepth + 1];        // all degrees below k are stored dense
+};
+
+// Builds the table; `top_only` selects the hybrid layout of the log operators.
+int make_level_table(int d, int depth, bool projected, const int64_t *level_sizes, const int64_t *words,
+                     bool top_only, LevelTable *out);
+
+// 1/n as a compile-time-foldable constant (n = 1..12).
+template <typename T>
+__host__ __device__ __forceinline__ constexpr T recip(int n) { return T(1) / T(n); }
+
+template <typename T> struct DType;
+template <> struct DType<float> { static constexpr int id = PSIG_F32; };
+template <> struct DType<double> { static constexpr int id = PSIG_F64; };
+
+// ---- launch entry points implemented in the .cu files (host functions) ----
+template <typename T>
+int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, T *out, cudaStream_t stream);
+template <typename T>
+int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, const T *sig, const T *grad,
+                         T *grad_path, T *inc_grad_ws, cudaStream_t stream);
+template <typename T>
+int generic_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, T *cache,
+                           cudaStream_t stream);
+template <typename T>
+int generic_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *cache,
+                            const T *grad_logsig, T *grad_sig, T *grad_cache_ws, cudaStream_t stream);
+
+// Register-tiled dense float32 kernels (tiled_sig.cu).  `supported` tells whether a kernel
+// exists for (d, depth).
+bool tiled_supported(int d, int depth);
+int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cudaStream_t stream);
+int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
+int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *sig, const float *grad,
+                       float *grad_path, void *workspace, cudaStream_t stream);
+
+inline int check_launch() { return cudaGetLastError() == cudaSuccess ? PSIG_OK : PSIG_ERR_CUDA; }
+
+}  // namespace psig

@@ -1,0 +1,460 @@
+// Generic signature kernels: any channel count d, any depth 1..12, dense or projected degrees,
+// windows, float32 and float64.
+//
+// Work decomposition (differs from the reference, which gives every word its own thread and
+// its own full prefix chain, src/pathsig/forward/sig_kernels.cu:95-157): one thread owns a
+// prefix u of length K-1 together with a tile of TB last letters, i.e. the TB words u.b of
+// degree K.  The Horner chain over the prefixes of u is evaluated once per step and shared by
+// the whole tile; a projected degree degenerates to tiles of one word.  All degrees of all
+// (path, window) units run in ONE launch: blockIdx.x selects degree and tile, blockIdx.y the
+// unit.  Increments are staged in shared memory a chunk of steps at a time, so the step loop
+// itself has no barrier and no global load.
+//
+// Backward is classical reverse mode on the thread-private chain: the prefix values are
+// rolled back one step by subtracting exactly what the forward step added, and the adjoints
+// of the prefixes are pushed through the transposed Horner chain, O(K^2) per step instead of
+// the O(K^3) two-sided formula of the reference
+// (src/pathsig/backward/sig_backward_kernels.cu:204-253).  Per-step increment gradients are
+// summed in shared memory and flushed to a zeroed (B, L-1, d) scratch with atomics, then
+// differenced into the path gradient (same data flow as
+// src/pathsig/backward/sig_backward_kernels.cu:256-318 and 347-377).
+#include "common.cuh"
+
+namespace psig {
+namespace {
+
+constexpr int kBlock = 128;
+constexpr size_t kStageBytes = 24 * 1024;
+
+struct GenericPlan {
+    LevelTable lt;
+    long long items[kMaxDepth + 1];        // thread items per degree
+    long long first_block[kMaxDepth + 2];  // first block of each degree inside a unit
+    int tiles;                             // letter tiles per dense prefix
+    int chunk;                             // steps staged per refill
+    long long B, L, W;                     // W >= 1
+    const int *windows;
+};
+
+template <typename T>
+__device__ __forceinline__ void kahan_add(T &sum, T add, T &comp)
+{
+    // Compensated summation; the explicit intrinsics keep the compiler from re-associating.
+    if constexpr (sizeof(T) == 4) {
+        const float y = __fsub_rn(add, comp);
+        const float t = __fadd_rn(sum, y);
+        comp = __fsub_rn(__fsub_rn(t, sum), y);
+        sum = t;
+    } else {
+        const double y = __dsub_rn(add, comp);
+        const double t = __dadd_rn(sum, y);
+        comp = __dsub_rn(__dsub_rn(t, sum), y);
+        sum = t;
+    }
+}
+
+struct Item {
+    long long u;   // code of the owned prefix (length K-1)
+    int b0;        // first last-letter of the tile
+    int nb;        // letters in the tile (0 = inactive thread)
+};
+
+template <int TB>
+__device__ __forceinline__ Item decode_item(const GenericPlan &p, int K, long long idx)
+{
+    Item it{0, 0, 0};
+    if (idx >= p.items[K]) return it;
+    const int d = p.lt.d;
+    if (p.lt.words[K] == nullptr) {
+        it.u = idx / p.tiles;
+        it.b0 = (int)(idx % p.tiles) * TB;
+        it.nb = min(TB, d - it.b0);
+    } else {
+        const long long code = p.lt.words[K][idx];
+        it.u = code / d;
+        it.b0 = (int)(code % d);
+        it.nb = 1;
+    }
+    return it;
+}
+
+__device__ __forceinline__ void unit_window(const GenericPlan &p, long long unit, long long &b, int &start, int &steps)
+{
+    b = unit / p.W;
+    const long long w = unit % p.W;
+    start = 0;
+    int end = (int)p.L;
+    if (p.windows) {
+        start = p.windows[2 * w];
+        end = p.windows[2 * w + 1];
+    }
+    steps = max(end - start - 1, 0);
+}
+
+// Stage increments c0 .. c0+n-1 of one unit: s_dx[t*d + a] = x[c0+t+1][a] - x[c0+t][a].
+template <typename T>
+__device__ __forceinline__ void stage_increments(const T *__restrict__ x, int d, int c0, int n, T *s_dx)
+{
+    const T *lo = x + (long long)c0 * d;
+    for (int i = threadIdx.x; i < n * d; i += kBlock) s_dx[i] = lo[i + d] - lo[i];
+}
+
+template <typename T, int K, int TB>
+__device__ void level_forward(const GenericPlan &p, long long unit, long long idx, const T *__restrict__ path,
+                              T *__restrict__ out, T *s_dx)
+{
+    const int d = p.lt.d;
+    const Item it = decode_item<TB>(p, K, idx);
+    int let[K > 1 ? K - 1 : 1];
+    {
+        long long c = it.u;
+#pragma unroll
+        for (int j = K - 2; j >= 0; --j) { let[j] = (int)(c % d); c /= d; }
+    }
+    long long b; int start, steps;
+    unit_window(p, unit, b, start, steps);
+    const T *x = path + (b * p.L + start) * d;
+
+    T pref[K], cpref[K];   // pref[j] = S(u[:j]), j = 1..K-1
+    T top[TB], ctop[TB];   // S(u.b) for the tile
+#pragma unroll
+    for (int j = 0; j < K; ++j) { pref[j] = T(0); cpref[j] = T(0); }
+#pragma unroll
+    for (int i = 0; i < TB; ++i) { top[i] = T(0); ctop[i] = T(0); }
+
+    for (int c0 = 0; c0 < steps; c0 += p.chunk) {
+        const int n = min(p.chunk, steps - c0);
+        __syncthreads();
+        stage_increments(x, d, c0, n, s_dx);
+        __syncthreads();
+        if (it.nb == 0) continue;
+        for (int t = 0; t < n; ++t) {
+            const T *dx = s_dx + t * d;
+            T xs[K > 1 ? K - 1 : 1];
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
+            // degree K: Horner chain over the prefixes of u, then one FMA per tile letter
+            T bc = T(1);
+#pragma unroll
+            for (int j = 1; j <= K - 1; ++j) bc = fma(bc, xs[j - 1] * recip<T>(K - j + 1), pref[j]);
+#pragma unroll
+            for (int i = 0; i < TB; ++i)
+                if (i < it.nb) kahan_add(top[i], bc * dx[it.b0 + i], ctop[i]);
+            // private copies of the lower prefixes, highest first so each reads old values
+#pragma unroll
+            for (int m = K - 1; m >= 1; --m) {
+                T bm = T(1);
+#pragma unroll
+                for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+                kahan_add(pref[m], bm * xs[m - 1], cpref[m]);
+            }
+        }
+    }
+    if (it.nb == 0) return;
+    T *row = out + unit * p.lt.total + p.lt.offset[K];
+    if (p.lt.words[K] == nullptr) {
+#pragma unroll
+        for (int i = 0; i < TB; ++i)
+            if (i < it.nb) row[it.u * d + it.b0 + i] = top[i];
+    } else {
+        row[idx] = top[0];
+    }
+}
+
+template <typename T, int K, int TB>
+__device__ void level_backward(const GenericPlan &p, long long unit, long long idx, const T *__restrict__ path,
+                               const T *__restrict__ sig, const T *__restrict__ grad, T *__restrict__ inc_grad,
+                               T *s_dx, T *s_gd)
+{
+    const int d = p.lt.d;
+    const Item it = decode_item<TB>(p, K, idx);
+    int let[K > 1 ? K - 1 : 1];
+    {
+        long long c = it.u;
+#pragma unroll
+        for (int j = K - 2; j >= 0; --j) { let[j] = (int)(c % d); c /= d; }
+    }
+    long long b; int start, steps;
+    unit_window(p, unit, b, start, steps);
+    if (steps == 0) return;  // uniform over the block
+    const T *x = path + (b * p.L + start) * d;
+    T *gd = inc_grad + (b * (p.L - 1) + start) * d;
+
+    T pref[K], apref[K];
+    T g[TB];
+#pragma unroll
+    for (int j = 0; j < K; ++j) { pref[j] = T(0); apref[j] = T(0); }
+#pragma unroll
+    for (int i = 0; i < TB; ++i) g[i] = T(0);
+
+    if (it.nb > 0) {
+        const T *grow = grad + unit * p.lt.total + p.lt.offset[K];
+        if (p.lt.words[K] == nullptr) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i)
+                if (i < it.nb) g[i] = grow[it.u * d + it.b0 + i];
+        } else {
+            g[0] = grow[idx];
+        }
+    }
+
+    // Prefix values at the end of the unit: read them from the saved signature while all
+    // lower degrees are stored dense, otherwise recompute them with a forward sweep.
+    if (p.lt.lower_dense[K]) {
+        if (it.nb > 0) {
+            const T *srow = sig + unit * p.lt.total;
+            long long c = it.u;
+#pragma unroll
+            for (int j = K - 1; j >= 1; --j) { pref[j] = srow[p.lt.dense_offset[j] + c]; c /= d; }
+        }
+    } else {
+        for (int c0 = 0; c0 < steps; c0 += p.chunk) {
+            const int n = min(p.chunk, steps - c0);
+            __syncthreads();
+            stage_increments(x, d, c0, n, s_dx);
+            __syncthreads();
+            if (it.nb == 0) continue;
+            for (int t = 0; t < n; ++t) {
+                const T *dx = s_dx + t * d;
+                T xs[K > 1 ? K - 1 : 1];
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
+#pragma unroll
+                for (int m = K - 1; m >= 1; --m) {
+                    T bm = T(1);
+#pragma unroll
+                    for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+                    pref[m] = fma(bm, xs[m - 1], pref[m]);
+                }
+            }
+        }
+    }
+
+    // Reverse sweep, chunk by chunk from the end.
+    const int nchunks = (steps + p.chunk - 1) / p.chunk;
+    for (int ci = nchunks - 1; ci >= 0; --ci) {
+        const int c0 = ci * p.chunk;
+        const int n = min(p.chunk, steps - c0);
+        __syncthreads();
+        stage_increments(x, d, c0, n, s_dx);
+        for (int i = threadIdx.x; i < n * d; i += kBlock) s_gd[i] = T(0);
+        __syncthreads();
+        if (it.nb > 0) {
+            for (int t = n - 1; t >= 0; --t) {
+                const T *dx = s_dx + t * d;
+                T *sg = s_gd + t * d;
+                T xs[K > 1 ? K - 1 : 1], lg[K > 1 ? K - 1 : 1];
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) { xs[j] = dx[let[j]]; lg[j] = T(0); }
+
+                // degrees 1..K-1 of the private chain: undo the step, then transpose it
+#pragma unroll
+                for (int m = 1; m <= K - 1; ++m) {
+                    T bc[K];  // bc[j] = Horner value after prefix length j (bc[0] = 1)
+                    bc[0] = T(1);
+#pragma unroll
+                    for (int j = 1; j <= m - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+                    pref[m] = fma(-bc[m - 1], xs[m - 1], pref[m]);
+                    const T a = apref[m];
+                    lg[m - 1] = fma(a, bc[m - 1], lg[m - 1]);
+                    T adj = a * xs[m - 1];
+#pragma unroll
+                    for (int j = m - 1; j >= 1; --j) {
+                        apref[j] += adj;
+                        const T c = recip<T>(m - j + 1);
+                        lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
+                        adj = adj * (xs[j - 1] * c);
+                    }
+                }
+                // degree K: the tile
+                {
+                    T bc[K];
+                    bc[0] = T(1);
+#pragma unroll
+                    for (int j = 1; j <= K - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(K - j + 1), pref[j]);
+                    T adj = T(0);
+#pragma unroll
+                    for (int i = 0; i < TB; ++i) {
+                        if (i < it.nb) {
+                            adj = fma(g[i], dx[it.b0 + i], adj);
+                            atomicAdd(&sg[it.b0 + i], g[i] * bc[K - 1]);
+                        }
+                    }
+#pragma unroll
+                    for (int j = K - 1; j >= 1; --j) {
+                        apref[j] += adj;
+                        const T c = recip<T>(K - j + 1);
+                        lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
+                        adj = adj * (xs[j - 1] * c);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) atomicAdd(&sg[let[j]], lg[j]);
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * d; i += kBlock) {
+            const T v = s_gd[i];
+            if (v != T(0)) atomicAdd(&gd[(long long)c0 * d + i], v);
+        }
+    }
+}
+
+#define PSIG_SWITCH_DEGREE(k, CALL)                                   \
+    switch (k) {                                                      \
+        case 1: { constexpr int K = 1; CALL; } break;                 \
+        case 2: { constexpr int K = 2; CALL; } break;                 \
+        case 3: { constexpr int K = 3; CALL; } break;                 \
+        case 4: { constexpr int K = 4; CALL; } break;                 \
+        case 5: { constexpr int K = 5; CALL; } break;                 \
+        case 6: { constexpr int K = 6; CALL; } break;                 \
+        case 7: { constexpr int K = 7; CALL; } break;                 \
+        case 8: { constexpr int K = 8; CALL; } break;                 \
+        case 9: { constexpr int K = 9; CALL; } break;                 \
+        case 10: { constexpr int K = 10; CALL; } break;               \
+        case 11: { constexpr int K = 11; CALL; } break;               \
+        default: { constexpr int K = 12; CALL; } break;               \
+    }
+
+__device__ __forceinline__ int block_degree(const GenericPlan &p)
+{
+    int k = 1;
+    while (k < p.lt.depth && (long long)blockIdx.x >= p.first_block[k + 1]) ++k;
+    return k;
+}
+
+template <typename T, int TB>
+__global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan p, const T *__restrict__ path,
+                                                              T *__restrict__ out)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *s_dx = reinterpret_cast<T *>(smem_raw);
+    const int k = block_degree(p);
+    const long long idx = ((long long)blockIdx.x - p.first_block[k]) * kBlock + threadIdx.x;
+    const long long units = p.B * p.W;
+    for (long long unit = blockIdx.y; unit < units; unit += gridDim.y) {
+        PSIG_SWITCH_DEGREE(k, (level_forward<T, K, TB>(p, unit, idx, path, out, s_dx)));
+    }
+}
+
+template <typename T, int TB>
+__global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan p, const T *__restrict__ path,
+                                                               const T *__restrict__ sig,
+                                                               const T *__restrict__ grad,
+                                                               T *__restrict__ inc_grad)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *s_dx = reinterpret_cast<T *>(smem_raw);
+    T *s_gd = s_dx + (size_t)p.chunk * p.lt.d;
+    const int k = block_degree(p);
+    const long long idx = ((long long)blockIdx.x - p.first_block[k]) * kBlock + threadIdx.x;
+    const long long units = p.B * p.W;
+    for (long long unit = blockIdx.y; unit < units; unit += gridDim.y) {
+        PSIG_SWITCH_DEGREE(k, (level_backward<T, K, TB>(p, unit, idx, path, sig, grad, inc_grad, s_dx, s_gd)));
+    }
+}
+
+// grad wrt increments -> grad wrt points (64-bit indexing).
+template <typename T>
+__global__ void increments_to_points(const T *__restrict__ inc_grad, T *__restrict__ path_grad, long long B,
+                                     long long L, int d)
+{
+    const long long total = B * L * d;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long b = i / (L * d);
+        const long long r = i - b * L * d;
+        const long long t = r / d;
+        const int a = (int)(r - t * d);
+        const T *g = inc_grad + b * (L - 1) * d + a;
+        const T after = (t < L - 1) ? g[t * d] : T(0);
+        const T before = (t > 0) ? g[(t - 1) * d] : T(0);
+        path_grad[i] = before - after;
+    }
+}
+
+template <typename T> constexpr int tile_letters() { return sizeof(T) == 4 ? 8 : 4; }
+
+template <typename T>
+int make_plan(const PsigSigDesc &desc, const LevelTable &lt, int buffers, GenericPlan *plan)
+{
+    constexpr int TB = tile_letters<T>();
+    GenericPlan &p = *plan;
+    p.lt = lt;
+    p.B = desc.B;
+    p.L = desc.L;
+    p.W = desc.W > 0 ? desc.W : 1;
+    p.windows = desc.W > 0 ? desc.windows : nullptr;
+    p.tiles = (lt.d + TB - 1) / TB;
+    long long blocks = 0;
+    long long d_pow = 1;  // d^(k-1)
+    for (int k = 1; k <= lt.depth; ++k) {
+        p.items[k] = lt.words[k] ? lt.size[k] : (lt.size[k] == 0 ? 0 : d_pow * p.tiles);
+        p.first_block[k] = blocks;
+        blocks += (p.items[k] + kBlock - 1) / kBlock;
+        if (k < lt.depth) d_pow *= lt.d;
+    }
+    for (int k = lt.depth + 1; k <= kMaxDepth + 1; ++k) p.first_block[k] = blocks;
+    if (blocks > 0x7fffffffLL) return PSIG_ERR_TOO_LARGE;
+    const size_t per_step = sizeof(T) * (size_t)lt.d * buffers;
+    if (per_step > 48 * 1024) return PSIG_ERR_TOO_LARGE;
+    long long chunk = (long long)(kStageBytes / per_step);
+    if (chunk < 1) chunk = 1;
+    if (chunk > 64) chunk = 64;
+    p.chunk = (int)chunk;
+    return PSIG_OK;
+}
+
+}  // namespace
+
+template <typename T>
+int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, T *out, cudaStream_t stream)
+{
+    constexpr int TB = tile_letters<T>();
+    GenericPlan plan;
+    const int rc = make_plan<T>(desc, lt, 1, &plan);
+    if (rc != PSIG_OK) return rc;
+    const long long units = plan.B * plan.W;
+    const long long blocks = plan.first_block[kMaxDepth + 1];
+    if (units == 0 || blocks == 0) return PSIG_OK;
+    const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
+    const size_t smem = sizeof(T) * (size_t)plan.chunk * lt.d;
+    sig_forward_generic<T, TB><<<grid, kBlock, smem, stream>>>(plan, path, out);
+    return check_launch();
+}
+
+template <typename T>
+int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, const T *sig, const T *grad,
+                         T *grad_path, T *inc_grad_ws, cudaStream_t stream)
+{
+    constexpr int TB = tile_letters<T>();
+    GenericPlan plan;
+    const int rc = make_plan<T>(desc, lt, 2, &plan);
+    if (rc != PSIG_OK) return rc;
+    const long long units = plan.B * plan.W;
+    const long long blocks = plan.first_block[kMaxDepth + 1];
+    if (desc.B == 0) return PSIG_OK;
+    const size_t inc_bytes = sizeof(T) * (size_t)desc.B * (size_t)(desc.L - 1) * lt.d;
+    if (cudaMemsetAsync(inc_grad_ws, 0, inc_bytes, stream) != cudaSuccess) return PSIG_ERR_CUDA;
+    if (units > 0 && blocks > 0) {
+        const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
+        const size_t smem = 2 * sizeof(T) * (size_t)plan.chunk * lt.d;
+        sig_backward_generic<T, TB><<<grid, kBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    }
+    const long long total = desc.B * desc.L * lt.d;
+    long long nb = (total + 255) / 256;
+    if (nb > 148 * 32) nb = 148 * 32;
+    increments_to_points<T><<<(unsigned)nb, 256, 0, stream>>>(inc_grad_ws, grad_path, desc.B, desc.L, lt.d);
+    return check_launch();
+}
+
+template int generic_sig_forward<float>(const PsigSigDesc &, const LevelTable &, const float *, float *, cudaStream_t);
+template int generic_sig_forward<double>(const PsigSigDesc &, const LevelTable &, const double *, double *,
+                                         cudaStream_t);
+template int generic_sig_backward<float>(const PsigSigDesc &, const LevelTable &, const float *, const float *,
+                                         const float *, float *, float *, cudaStream_t);
+template int generic_sig_backward<double>(const PsigSigDesc &, const LevelTable &, const double *, const double *,
+                                          const double *, double *, double *, cudaStream_t);
+
+}  // namespace psig

@@ -1,0 +1,120 @@
+"""``Signature`` and ``LogSignature`` modules: the user-facing API.
+
+Host-side mirror of the reference's ``src/pathsig/modules.py``: keyword-only ``depth``,
+``projection`` and ``windows``; the same argument checks and exception types
+(``modules.py:10-38``); the same buffer names and persistence, so a reference ``state_dict``
+loads (``_windows``, ``_encoded_words``, ``_top_words``, ``_indices_from_sig``,
+``modules.py:54-59, 84-110``); the same output shapes ``(B, D)`` / ``(B, W, D)``.
+
+``LogSignature`` keeps the reference's composition (``modules.py:112-135``): signature in the
+hybrid layout (dense degrees below ``depth``, projected top degree), tensor logarithm in word
+coordinates, then a column gather for the projected case.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .ops import compute_signature, sig_to_logsig
+from .projections import _default_device
+
+_MAX_DEPTH = 12
+
+
+def _checked_depth(depth: int) -> int:
+    if not (1 <= depth <= _MAX_DEPTH):
+        raise ValueError("depth must satisfy 1 <= depth <= 12.")
+    return depth
+
+
+def _window_buffer(windows: Optional[torch.Tensor]) -> Tuple[bool, torch.Tensor]:
+    """(use_windows, contiguous int32 (W, 2) buffer); an empty (0, 2) buffer when unused."""
+    if windows is None:
+        return False, torch.empty((0, 2), dtype=torch.int32, device=_default_device())
+    if windows.device.type != "cuda":
+        raise TypeError("windows must be a CUDA tensor.")
+    if windows.dim() != 2 or windows.size(1) != 2:
+        raise TypeError("windows must have shape [num_windows, 2].")
+    if windows.dtype not in (torch.int32, torch.int64):
+        raise TypeError("windows must have dtype int32 or int64.")
+    return True, windows.contiguous().to(dtype=torch.int32)
+
+
+def _projection_words(projection) -> Tuple[bool, Optional[torch.Tensor]]:
+    if projection is None:
+        return False, None
+    words = projection.encoded_words
+    if words.device.type != "cuda" or words.dtype != torch.int64 or words.dim() != 1:
+        raise TypeError("projection.encoded_words must be a 1D CUDA int64 tensor.")
+    return True, words.contiguous()
+
+
+def _no_words() -> torch.Tensor:
+    return torch.empty(0, dtype=torch.int64, device=_default_device())
+
+
+class Signature(nn.Module):
+    """Truncated signature of a batch of paths ``(B, L, d)`` -> ``(B, D)`` or ``(B, W, D)``."""
+
+    def __init__(self, *, depth: int, projection=None, windows=None):
+        super().__init__()
+        self.depth = _checked_depth(depth)
+        self.projection = projection
+        self.alternative_projection, words = _projection_words(projection)
+        self.use_windows, window_buffer = _window_buffer(windows)
+        self.register_buffer("_windows", window_buffer, persistent=self.use_windows)
+        self.register_buffer("_encoded_words", words if self.alternative_projection else _no_words(),
+                             persistent=self.alternative_projection)
+        self._level_sizes: List[int] = projection.level_sizes if self.alternative_projection else []
+
+    def forward(self, path: torch.Tensor) -> torch.Tensor:
+        return compute_signature(path, self.depth, self.alternative_projection, self._encoded_words,
+                                 self._level_sizes, self.use_windows, self._windows)
+
+
+class LogSignature(nn.Module):
+    """Truncated log-signature in word coordinates (optionally projected, optionally windowed)."""
+
+    def __init__(self, *, depth: int, projection=None, windows=None):
+        super().__init__()
+        self.depth = _checked_depth(depth)
+        self.projection = projection
+        self.alternative_projection, words = _projection_words(projection)
+        self.use_windows, window_buffer = _window_buffer(windows)
+        self.register_buffer("_windows", window_buffer, persistent=self.use_windows)
+
+        if not self.alternative_projection:
+            for name in ("_encoded_words", "_top_words", "_indices_from_sig"):
+                self.register_buffer(name, _no_words(), persistent=False)
+            self._level_sizes: List[int] = []
+            self._ext_level_sizes: List[int] = []
+            return
+
+        self.register_buffer("_encoded_words", words, persistent=True)
+        self._level_sizes = projection.level_sizes
+        d = self._path_dim = int(projection.path_dim)
+
+        # The log needs every word below the top degree, so those degrees are computed dense;
+        # only the top degree stays projected.  Its codes are the tail of encoded_words.
+        explicit_below_top = sum(self._level_sizes[k] for k in range(1, self.depth)
+                                 if self._level_sizes[k] != d ** k)
+        self.register_buffer("_top_words", words[explicit_below_top:], persistent=True)
+        self._ext_level_sizes = [0] + [d ** k for k in range(1, self.depth)] + [int(self._level_sizes[self.depth])]
+        columns = projection.logsig_indices().to(device=words.device, dtype=torch.int64).contiguous()
+        self.register_buffer("_indices_from_sig", columns, persistent=True)
+
+    def forward(self, path: torch.Tensor) -> torch.Tensor:
+        if self.alternative_projection:
+            d = self._path_dim
+            level_sizes = self._ext_level_sizes
+        else:
+            d = int(path.shape[-1])
+            level_sizes = [0] + [d ** k for k in range(1, self.depth + 1)]
+        sig = compute_signature(path, self.depth, self.alternative_projection, self._top_words, level_sizes,
+                                self.use_windows, self._windows)
+        logsig, _ = sig_to_logsig(sig, self.depth, d, self.alternative_projection, self._top_words, level_sizes)
+        if not self.alternative_projection:
+            return logsig
+        return logsig.index_select(dim=-1, index=self._indices_from_sig.to(logsig.device))
