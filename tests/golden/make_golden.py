@@ -92,7 +92,7 @@ def main():
              top_size=len(lyndon_codes(4, 5)))
 
     os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
-    meta = dict(torch=torch.__version__, device=torch.cuda.get_device_name(0),
+    meta = dict(torch=str(torch.__version__), device=torch.cuda.get_device_name(0),
                 source="reference CUDA operators (torch.ops.pathsig) compiled unchanged by oracle/build_ref.py")
     torch.save(dict(meta=meta, cases=cases), args.out)
     print("wrote", args.out, "with", len(cases), "cases")

@@ -137,8 +137,8 @@ def test_zero_batch_and_errors(ps):
         sig(torch.zeros(2, 1, 2, device=DEV))          # fewer than 2 points
     with pytest.raises(RuntimeError):
         sig(torch.zeros(2, 5, 2, device=DEV, dtype=torch.float16))
-    with pytest.raises(NotImplementedError):
-        sig(torch.zeros(2, 5, 2))                      # CPU tensor: no CPU implementation
+    with pytest.raises(RuntimeError):
+        sig(torch.zeros(2, 5, 2))                      # CPU tensor: there is no CPU implementation
     with pytest.raises(ValueError):
         ps.Signature(depth=13)
     with pytest.raises(TypeError):
