@@ -177,3 +177,31 @@ def test_reference_build_agrees(ps, oracle):
         ours_gs = ps.ops.logsig_backward(ours, ours_c, g, 4, False, empty_w, ls)
         theirs_gs = ref.logsig_backward(theirs, theirs_c, g, 4, False, empty_w, ls)
         assert util.rel_error(ours_gs, theirs_gs) < util.TOL[dtype]
+
+
+# ---- register-tiled kernels (float32, dense) ----
+
+TILED = [(8, 4), (16, 4), (16, 3), (4, 6)]
+
+
+@pytest.mark.parametrize("d,depth", TILED)
+@pytest.mark.parametrize("L", [2, 3, 34, 101])
+def test_tiled_signature(ps, oracle, d, depth, L):
+    x = util.brownian_path(3, L, d, seed=L + d, dtype=torch.float32)
+    _run_sig(ps, oracle, x, depth, algo="tiled")
+
+
+@pytest.mark.parametrize("d,depth", TILED)
+def test_tiled_windows(ps, oracle, d, depth):
+    x = util.brownian_path(2, 70, d, seed=d, dtype=torch.float32)
+    win = torch.tensor([[0, 70], [5, 7], [10, 50], [3, 3], [12, 13], [20, 70], [0, 41], [33, 66]], dtype=torch.int32)
+    _run_sig(ps, oracle, x, depth, windows=win, algo="tiled")
+
+
+def test_tiled_unsupported_shape_is_an_error(ps):
+    ps.ops.set_algorithm("tiled")
+    try:
+        with pytest.raises(RuntimeError):
+            ps.Signature(depth=5)(torch.zeros(1, 4, 3, device=DEV))
+    finally:
+        ps.ops.set_algorithm("auto")
