@@ -1,0 +1,589 @@
+#!/usr/bin/env python
+"""Benchmark of the signature hot path: paths*steps/s for forward+backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the hot path over one batch of seeded synthetic
+Brownian paths.  The default workload (``cfg2``) is the windowed depth-4 signature of
+(256, 1024, 8) float32 paths over 61 sliding windows [16k, 16k+64); under ``torchrun`` every
+rank processes its own batch of that size (weak scaling, no collective on the data path).
+
+The JSON line printed by rank 0 carries: ``value`` (device-timed, inputs resident in HBM),
+``e2e`` (same metric through ``pathsig_b200.Signature`` with pinned-host inputs, H2D and D2H
+copies inside the timed region), ``roofline`` (FP32 FMA bound kernels: algorithmic FLOP of the
+backward operator over its measured duration, against an FFMA peak measured in the same
+process), ``roofline_hbm``, ``cpu_baseline`` (the CPU oracle on a bounded sample), ``clocks``
+and ``others`` (the remaining workloads of the baseline specification, short runs).
+
+``--impl reference`` times the CPU restatement of the reference algorithm (``oracle/``) on the
+host cores instead; the reference itself has no CPU implementation.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "paths*steps/s, forward+backward"
+UNIT = "paths*steps/s"
+
+# DRAM traffic of one launch of the dominant kernel, from ncu captures summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+# ----------------------------------------------------------------------------------------------
+# workloads (BASELINE.json configs 1-5)
+# ----------------------------------------------------------------------------------------------
+
+def _brownian(B, L, d, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.cumsum(torch.randn(B, L, d, generator=g, dtype=torch.float64) / math.sqrt(L), dim=1)
+    return x.to(torch.float32)
+
+
+def _normal(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(tuple(shape), generator=g, dtype=torch.float32)
+
+
+def _random_words(n_words, d, min_len, max_len, seed):
+    import random
+    rng = random.Random(seed)
+    seen = set()
+    while len(seen) < n_words:
+        n = rng.randint(min_len, max_len)
+        seen.add(tuple(rng.randrange(d) for _ in range(n)))
+    return sorted(seen, key=lambda w: (len(w), w))
+
+
+def _dense_fma(d, depth):
+    return sum((depth - j + 1) * d ** j for j in range(1, depth + 1))
+
+
+def _closure_fma(words_by_level, d, depth, dense_levels=()):
+    """FMAs per path*step of the shared-prefix Horner scheme for a projected state set:
+    sum over target degrees k of the number of distinct non-empty prefixes of the degree-k
+    state words (requested words and the prefixes of longer requested words)."""
+    requested = set()
+    for ws in words_by_level.values():
+        requested.update(ws)
+    total = 0
+    for k in range(1, depth + 1):
+        if k in dense_levels:
+            total += sum(d ** j for j in range(1, k + 1))
+            continue
+        state_k = {w[:k] for w in requested if len(w) >= k}
+        prefixes = set()
+        for w in state_k:
+            for j in range(1, k + 1):
+                prefixes.add(w[:j])
+        total += len(prefixes)
+    return total
+
+
+SPECS = {
+    "cfg1": dict(kind="sig", B=32, L=128, d=8, depth=4, desc="Signature depth 4, (32,128,8)"),
+    "cfg2": dict(kind="sig", B=256, L=1024, d=8, depth=4, windows=(64, 16, 61),
+                 desc="Signature depth 4, (256,1024,8), 61 windows [16k,16k+64)"),
+    "cfg3": dict(kind="words", B=512, L=512, d=8, depth=6, n_words=200,
+                 desc="Signature depth 6, (512,512,8), level 1 + 200 seeded words"),
+    "cfg4": dict(kind="loglyndon", B=1024, L=256, d=4, depth=6,
+                 desc="LogSignature depth 6, (1024,256,4), Lyndon projection"),
+    "cfg5": dict(kind="sig", B=4096, L=2048, d=16, depth=4, desc="Signature depth 4, (4096,2048,16), batch-sharded"),
+}
+
+
+class Workload:
+    """One configuration: inputs, module, step functions and work accounting."""
+
+    def __init__(self, name, B=None, seed=0):
+        self.name = name
+        s = dict(SPECS[name])
+        if B is not None:
+            s["B"] = B
+        self.spec = s
+        self.B, self.L, self.d, self.depth = s["B"], s["L"], s["d"], s["depth"]
+        self.seed = seed
+        self.windows = None
+        if "windows" in s:
+            length, stride, count = s["windows"]
+            self.windows = torch.tensor([[stride * k, stride * k + length] for k in range(count)], dtype=torch.int32)
+            self.steps_per_path = count * (length - 1)
+        else:
+            self.steps_per_path = self.L - 1
+        self.units = self.B * self.steps_per_path
+        self.words = None
+        if s["kind"] == "words":
+            self.words = [(a,) for a in range(self.d)] + _random_words(s["n_words"], self.d, 2, self.depth, seed=1234)
+            by_level = {}
+            for w in self.words:
+                by_level.setdefault(len(w), []).append(w)
+            self.fma_fwd = _closure_fma(by_level, self.d, self.depth)
+        elif s["kind"] == "loglyndon":
+            from pathsig_b200.projections import lyndon_words
+            top = lyndon_words(self.d, self.depth)
+            letters = []
+            for c in top:
+                w = []
+                for _ in range(self.depth):
+                    w.append(c % self.d)
+                    c //= self.d
+                letters.append(tuple(reversed(w)))
+            self.fma_fwd = _closure_fma({self.depth: letters}, self.d, self.depth,
+                                        dense_levels=tuple(range(1, self.depth)))
+        else:
+            self.fma_fwd = _dense_fma(self.d, self.depth)
+
+    # ---- host data ----
+    def host_path(self):
+        return _brownian(self.B, self.L, self.d, self.seed)
+
+    def out_width(self, mod):
+        if self.spec["kind"] == "sig":
+            return sum(self.d ** k for k in range(1, self.depth + 1))
+        return mod.projection.sig_size
+
+    def flop_fwd_bwd(self):
+        return 8.0 * self.fma_fwd * self.units  # forward F FMAs, backward credited 3F
+
+    def flop_bwd(self):
+        return 6.0 * self.fma_fwd * self.units
+
+    def flop_fwd(self):
+        return 2.0 * self.fma_fwd * self.units
+
+    # ---- device objects ----
+    def build(self, device):
+        import pathsig_b200 as ps
+        kind = self.spec["kind"]
+        win = None if self.windows is None else self.windows.to(device)
+        if kind == "sig":
+            mod = ps.Signature(depth=self.depth, windows=win)
+        elif kind == "words":
+            proj = ps.projections.words([w for w in self.words if len(w) > 1], self.depth, self.d, full_levels=(1,),
+                                        device=device)
+            mod = ps.Signature(depth=self.depth, projection=proj)
+        else:
+            proj = ps.projections.lyndon(self.depth, self.d, device=device)
+            mod = ps.LogSignature(depth=self.depth, projection=proj)
+        self.mod = mod.to(device)
+        self.x = self.host_path().to(device)
+        W = () if self.windows is None else (self.windows.shape[0],)
+        self.G = _normal((self.B,) + W + (self.out_width(mod),), self.seed + 1).to(device)
+        self.bytes_fwd = self.x.numel() * 4 + self.G.numel() * 4
+        self.bytes_fwd_bwd = 2 * self.x.numel() * 4 + 2 * self.G.numel() * 4
+        return self
+
+    def step_forward(self):
+        with torch.no_grad():
+            return self.mod(self.x)
+
+    def step_fwd_bwd(self, events=None):
+        """Forward + backward with dL/dout = G (the loss is sum(out * G)).  For the signature
+        modules the two operators are called directly; returns grad wrt the path."""
+        import pathsig_b200 as ps
+        m = self.mod
+        if isinstance(m, ps.Signature):
+            sig = ps.ops.compute_signature(self.x, m.depth, m.alternative_projection, m._encoded_words,
+                                           m._level_sizes, m.use_windows, m._windows)
+            if events is not None:
+                events[0].record()
+            gp = ps.ops.signature_backward(self.x, sig, self.G, m.depth, m.alternative_projection,
+                                           m._encoded_words, m._level_sizes, m.use_windows, m._windows)
+            if events is not None:
+                events[1].record()
+            return gp
+        x = self.x.detach().requires_grad_(True)
+        out = m(x)
+        if events is not None:
+            events[0].record()
+        out.backward(self.G)
+        if events is not None:
+            events[1].record()
+        return x.grad
+
+    def kernels_per_step(self):
+        import pathsig_b200 as ps
+        if isinstance(self.mod, ps.Signature):
+            scratch = self.windows is not None or (self.d, self.depth) in ((16, 4), (16, 3)) \
+                or self.spec["kind"] != "sig"
+            return 1 + 1 + (1 if scratch else 0)
+        return 1 + 1 + 1 + 1 + 1  # sig fwd, log fwd, log bwd, sig bwd, increments->points
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+                power.append(float(r[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c, p in zip(sm, power) if p >= 0.5 * max(power)] if power else sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# measurement helpers
+# ----------------------------------------------------------------------------------------------
+
+def _dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def _barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _max_over_ranks(value, world, device):
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, warmup, world, device):
+    """Device time (ms, max over ranks) of exactly `steps` calls of fn after `warmup` calls."""
+    for _ in range(warmup):
+        fn()
+    _barrier(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    _barrier(world)
+    return _max_over_ranks(start.elapsed_time(end), world, device)
+
+
+def measure_fp32_peak(device):
+    """TFLOP/s of a register-only FFMA loop (psig_probe_fp32_fma), best of 5."""
+    import ctypes
+    from pathsig_b200 import _load
+    lib = _load.ensure_loaded()
+    scratch = torch.zeros(16, device=device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    best = 0.0
+    for it in range(6):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fmas = lib.psig_probe_fp32_fma(sms * 8, 20000, ctypes.c_void_p(scratch.data_ptr()), stream)
+        e.record()
+        torch.cuda.synchronize()
+        if it > 0:
+            best = max(best, 2.0 * fmas / (s.elapsed_time(e) * 1e-3) / 1e12)
+    return best
+
+
+def cpu_baseline(name, threads=None, seconds_hint=15.0):
+    """The CPU oracle (a port of the reference algorithm) on a bounded sample of the workload."""
+    from oracle import oracle
+    cores = threads or os.cpu_count() or 1
+    oracle.set_threads(cores)
+    spec = SPECS[name]
+    B = min(spec["B"], 2 * cores if name != "cfg5" else cores)
+    wl = Workload(name, B=B)
+    x = wl.host_path()
+    win = wl.windows
+    kind = spec["kind"]
+    t0 = time.perf_counter()
+    if kind == "loglyndon":
+        from pathsig_b200.projections import projections
+        proj = projections.lyndon(wl.depth, wl.d, device="cpu")
+        top = proj.encoded_words[sum(proj.level_sizes[k] for k in range(1, wl.depth)
+                                     if proj.level_sizes[k] != wl.d ** k):]
+        ext = [0] + [wl.d ** k for k in range(1, wl.depth)] + [proj.level_sizes[wl.depth]]
+        idx = proj.logsig_indices()
+        g = _normal((B, proj.sig_size), 1)
+        oracle.logsignature(x, wl.depth, top_words=top, ext_level_sizes=ext, indices=idx, grad_out=g)
+    else:
+        ew = ls = None
+        if kind == "words":
+            from pathsig_b200.projections import projections
+            proj = projections.words([w for w in wl.words if len(w) > 1], wl.depth, wl.d, full_levels=(1,), device="cpu")
+            ew, ls = proj.encoded_words, proj.level_sizes
+        sig = oracle.sig_forward(x, wl.depth, ew, ls, win)
+        g = _normal(sig.shape, 1)
+        oracle.sig_backward(x, sig, g, wl.depth, ew, ls, win)
+    dt = time.perf_counter() - t0
+    return {"value": wl.units / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{name} with B={B} of {spec['B']} paths, float32, one forward+backward, {dt:.2f} s wall "
+                      f"(work is linear in B); port of the reference per-word algorithm, OpenMP over paths"}, dt
+
+
+# ----------------------------------------------------------------------------------------------
+# arms
+# ----------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_baseline(name)
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last, _dt = cpu_baseline(name)
+    total = time.perf_counter() - t0
+    spec = SPECS[name]
+    B = min(spec["B"], 2 * last["cores"] if name != "cfg5" else last["cores"])
+    units = Workload(name, B=B).units
+    value = units * args.steps / total
+    last["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{name}: {spec['desc']}; CPU sample B={B}", "timing": "host wall clock"},
+        "cpu_baseline": last,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference has no CPU implementation (CUDA-only operators); this arm times the CPU "
+                "restatement of its algorithm (oracle/) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e2e=False, fp32_peak=None):
+    import pathsig_b200 as ps
+    wl = Workload(name, B=per_rank_B, seed=int(os.environ.get("RANK", "0"))).build(device)
+    res = {"workload": name}
+    # forward only
+    ms_f = time_steps(wl.step_forward, steps, warmup, world, device)
+    # forward + backward, with the backward operator bracketed by events
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    it = iter(pairs)
+
+    def step():
+        wl.step_fwd_bwd(next(it, None))
+
+    for _ in range(warmup):
+        wl.step_fwd_bwd()
+    _barrier(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    _barrier(world)
+    ms_fb = _max_over_ranks(start.elapsed_time(end), world, device)
+    bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+    total_units = wl.units * world
+    res.update({
+        "units_per_step": total_units,
+        "fma_per_unit_fwd": wl.fma_fwd,
+        "fwd": {"value": total_units * steps / (ms_f * 1e-3), "ms_per_step": ms_f / steps},
+        "fwd_bwd": {"value": total_units * steps / (ms_fb * 1e-3), "ms_per_step": ms_fb / steps},
+        "bwd_op_ms": bwd_ms,
+        "tflops_fwd": wl.flop_fwd() * world / (ms_f / steps * 1e-3) / 1e12,
+        "tflops_fwd_bwd": wl.flop_fwd_bwd() * world / (ms_fb / steps * 1e-3) / 1e12,
+        "hbm_gbs_fwd_bwd": wl.bytes_fwd_bwd * world / (ms_fb / steps * 1e-3) / 1e9,
+        "kernels_per_step": wl.kernels_per_step(),
+    })
+    if fp32_peak:
+        res["frac_fp32_peak_fwd_bwd"] = res["tflops_fwd_bwd"] / (fp32_peak * world)
+        res["frac_fp32_peak_fwd"] = res["tflops_fwd"] / (fp32_peak * world)
+    res["_wl"] = wl
+    if with_e2e:
+        xh = wl.host_path().pin_memory()
+        gh = torch.empty_like(xh).pin_memory()
+        lh = torch.empty(1, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            x = xh.to(device, non_blocking=True).requires_grad_(True)
+            out = wl.mod(x)
+            loss = (out * wl.G).sum()
+            loss.backward()
+            gh.copy_(x.grad, non_blocking=True)
+            lh.copy_(loss.detach().reshape(1), non_blocking=True)
+
+        ms_e = time_steps(e2e_step, steps, warmup, world, device)
+        res["e2e"] = {"value": total_units * steps / (ms_e * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": xh.numel() * 4 * world, "d2h_bytes_per_step": (gh.numel() + 1) * 4 * world,
+                      "ms_per_step": ms_e / steps,
+                      "api": "pathsig_b200.Signature(...)(x); (out*G).sum().backward(); grad and loss copied to pinned host"}
+    return res
+
+
+def run_ours(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    world, rank, local = _dist_setup(args.gpus)
+    device = torch.device("cuda", local if world > 1 else 0)
+    import pathsig_b200  # noqa: F401
+
+    fp32_peak = measure_fp32_peak(device)
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    hbm_peak, hbm_src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
+
+    name = args.workload
+    sampler = ClockSampler(local if world > 1 else 0)
+    if rank == 0:
+        sampler.start()
+    t_begin = time.perf_counter()
+    main = measure_workload(name, args.steps, args.warmup, world, device, with_e2e=True, fp32_peak=fp32_peak)
+    # keep the same step running long enough for the 100 ms clock sampler to see it under load
+    wl = main["_wl"]
+    while time.perf_counter() - t_begin < 2.0:
+        for _ in range(20):
+            wl.step_fwd_bwd()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["sampled_over"] = "timed regions plus continuation of the same step up to 2 s"
+
+    others = {}
+    if not args.no_others:
+        for other in SPECS:
+            if other == name:
+                continue
+            B = None
+            if other == "cfg5":
+                B = SPECS["cfg5"]["B"] // world  # strong scaling: the 4096 paths are sharded over the ranks
+            r = measure_workload(other, max(3, min(args.steps, 5)), 2, world, device, per_rank_B=B, fp32_peak=fp32_peak)
+            r.pop("_wl")
+            if other == "cfg5":
+                r["scaling"] = "strong"
+            others[other] = r
+            torch.cuda.empty_cache()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, _ = cpu_baseline(name)
+
+    if rank != 0:
+        return
+    main.pop("_wl")
+    spec = SPECS[name]
+    steps = args.steps
+    bwd_flop = wl.flop_bwd()
+    achieved = bwd_flop / (main["bwd_op_ms"] * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": main["fwd_bwd"]["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": main["fwd_bwd"]["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{name}: {spec['desc']}", "per_gpu_batch": spec["B"], "global_batch": spec["B"] * world,
+                   "units_per_step": main["units_per_step"], "l2": "inputs_larger_than_l2"
+                   if wl.bytes_fwd_bwd > 126e6 else "inputs smaller than L2 (latency-bound configuration)",
+                   "parallelism": f"batch shards x{world}, no collective"},
+        "forward_only": main["fwd"],
+        "clocks": clocks,
+        "e2e": main["e2e"],
+        "gpu_launches": steps * main["kernels_per_step"],
+        "roofline": {
+            "bound": "fp32_fma", "kernel": "signature_backward operator (sig_backward_tiled + increments_to_points)",
+            "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
+            "peak_source": "psig_probe_fp32_fma measured in this process (MEASURED_PEAKS.json has no FP32 figure)",
+            "flop_per_launch": bwd_flop, "flop_convention": "backward credited 3 x F_fwd FMAs per path*step",
+            "traffic": NCU_TRAFFIC_BYTES.get(name),
+            "whole_step": {"achieved": main["tflops_fwd_bwd"], "frac": main["tflops_fwd_bwd"] / (fp32_peak * world)},
+        },
+        "roofline_hbm": {"bound": "hbm", "achieved": main["hbm_gbs_fwd_bwd"], "peak": hbm_peak * world if hbm_peak else None,
+                         "unit": "GB/s", "frac": main["hbm_gbs_fwd_bwd"] / (hbm_peak * world) if hbm_peak else None,
+                         "peak_source": hbm_src, "bytes": "read path + write signature + read grad + write grad_path"},
+        "cpu_baseline": cpu,
+        "others": others,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg2", choices=sorted(SPECS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the short runs of the other workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -128,6 +128,12 @@ int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
 int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,
                          void *grad_sig, void *workspace, int64_t workspace_bytes, void *stream);
 
+/* Measurement aid with no counterpart in the reference: launches `blocks` x 256 threads that each
+ * run `iters` x 128 dependent-chain-free FP32 FMAs on registers only, and returns the number of
+ * FMAs issued (or a negative PsigStatus).  Timed by the caller, it gives the FP32 FMA peak used
+ * as the roofline denominator.  `scratch` must point to at least 4 bytes of device memory. */
+int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

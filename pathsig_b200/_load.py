@@ -68,6 +68,7 @@ EXPORTS = {
     "psig_logsig_forward": (_int, [_LogP, _vp, _vp, _vp, _vp]),
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "psig_probe_fp32_fma": (_i64, [_int, _int, _vp, _vp]),
 }
 
 

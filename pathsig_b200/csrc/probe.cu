@@ -1,0 +1,36 @@
+// Measurement aid: a register-only FP32 FMA loop used by bench.py to measure the FFMA peak of
+// the device it runs on (the roofline denominator of the signature kernels).
+#include "common.cuh"
+
+namespace psig {
+namespace {
+
+__global__ void __launch_bounds__(256) ffma_probe(float *out, int iters, float a, float b)
+{
+    float r[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = (float)(threadIdx.x + i) * 1e-3f;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int rep = 0; rep < 8; ++rep) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = fmaf(r[i], a, b);
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s += r[i];
+    if (s == 12345.678f) out[0] = s;  // keeps the loop alive without a store in practice
+}
+
+}  // namespace
+}  // namespace psig
+
+extern "C" int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream)
+{
+    if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
+    psig::ffma_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
+                                                                          0.999999f, 1e-7f);
+    if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    return (int64_t)blocks * 256 * (int64_t)iters * 8 * 16;  // FMAs issued
+}
