@@ -218,9 +218,8 @@ class Workload:
     def kernels_per_step(self):
         import pathsig_b200 as ps
         if isinstance(self.mod, ps.Signature):
-            scratch = self.windows is not None or (self.d, self.depth) in ((16, 4), (16, 3)) \
-                or self.spec["kind"] != "sig"
-            return 1 + 1 + (1 if scratch else 0)
+            generic = self.spec["kind"] != "sig"  # generic backward adds the increments->points kernel
+            return 1 + 1 + (1 if generic else 0)
         return 1 + 1 + 1 + 1 + 1  # sig fwd, log fwd, log bwd, sig bwd, increments->points
 
 
@@ -485,6 +484,13 @@ def run_ours(args):
     device = torch.device("cuda", local if world > 1 else 0)
     import pathsig_b200  # noqa: F401
 
+    if args.profile:
+        wl = Workload(args.workload, B=args.batch).build(device)
+        for _ in range(args.warmup + args.steps):
+            wl.step_fwd_bwd()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_run": args.workload, "batch": wl.B, "passes": args.warmup + args.steps}))
+        return
     fp32_peak = measure_fp32_peak(device)
     peaks = {}
     try:
@@ -499,7 +505,8 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     t_begin = time.perf_counter()
-    main = measure_workload(name, args.steps, args.warmup, world, device, with_e2e=True, fp32_peak=fp32_peak)
+    main = measure_workload(name, args.steps, args.warmup, world, device, per_rank_B=args.batch, with_e2e=True,
+                            fp32_peak=fp32_peak)
     # keep the same step running long enough for the 100 ms clock sampler to see it under load
     wl = main["_wl"]
     while time.perf_counter() - t_begin < 2.0:
@@ -540,7 +547,7 @@ def run_ours(args):
         "metric": METRIC, "value": main["fwd_bwd"]["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": main["fwd_bwd"]["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{name}: {spec['desc']}", "per_gpu_batch": spec["B"], "global_batch": spec["B"] * world,
+        "config": {"workload": f"{name}: {spec['desc']}", "per_gpu_batch": wl.B, "global_batch": wl.B * world,
                    "units_per_step": main["units_per_step"], "l2": "inputs_larger_than_l2"
                    if wl.bytes_fwd_bwd > 126e6 else "inputs smaller than L2 (latency-bound configuration)",
                    "parallelism": f"batch shards x{world}, no collective"},
@@ -574,8 +581,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the short runs of the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch of the workload")
+    ap.add_argument("--profile", action="store_true",
+                    help="only run warmup+steps forward+backward passes of the workload (for ncu captures)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "ours" and not args.profile:
+        args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
     else:

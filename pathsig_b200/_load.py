@@ -12,7 +12,8 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libpathsig_b200.so"
-LIB_PATH = os.path.join(_HERE, LIB_NAME)
+# PATHSIG_B200_LIB selects another build of the same library (kernel tuning experiments).
+LIB_PATH = os.environ.get("PATHSIG_B200_LIB") or os.path.join(_HERE, LIB_NAME)
 MAX_DEPTH = 12
 ABI_VERSION = 1
 

@@ -25,6 +25,13 @@
 // global atomics every step (src/pathsig/backward/sig_backward_kernels.cu:204-318).
 #include "common.cuh"
 
+#ifndef PSIG_FWD_PREFETCH
+#define PSIG_FWD_PREFETCH 0
+#endif
+#ifndef PSIG_BWD_PREFETCH
+#define PSIG_BWD_PREFETCH 0
+#endif
+
 namespace psig {
 namespace {
 
@@ -112,15 +119,108 @@ __device__ __forceinline__ void stage_scaled_increments(const float *__restrict_
     }
 }
 
+// The operands one step needs: the increment at this thread's prefix letters, the full
+// increment vector, and the (scaled) slices at the owned first letters.
+template <int D, int DA, int P, int Q>
+struct StepOperands {
+    float xs[P];
+    float dxf1[D];                      // dx
+    float dxa1[DA];                     // dx[a0..]
+    float dxa2[Q >= 2 ? DA : 1];        // dx[a0..] / 2
+    float dxa3[Q >= 3 ? DA : 1];        // dx[a0..] / 3
+    float dxf2[Q >= 3 ? D : 1];         // dx / 2
+};
+
+template <int D, int DA, int P, int Q, int CH>
+__device__ __forceinline__ void load_operands(StepOperands<D, DA, P, Q> &o, const float (*s_dx)[CH][D], int t,
+                                              const int (&let)[P], int a0)
+{
+    const float *row = s_dx[0][t];
+#pragma unroll
+    for (int j = 0; j < P; ++j) o.xs[j] = row[let[j]];
+    load_run<D>(o.dxf1, row, true);
+    if constexpr (DA == D) {
+#pragma unroll
+        for (int a = 0; a < DA; ++a) o.dxa1[a] = o.dxf1[a];
+    } else {
+        load_run<DA>(o.dxa1, row + a0, true);
+    }
+    if constexpr (Q >= 2) load_run<DA>(o.dxa2, s_dx[1][t] + a0, true);
+    if constexpr (Q >= 3) {
+        load_run<DA>(o.dxa3, s_dx[2][t] + a0, true);
+        load_run<D>(o.dxf2, s_dx[1][t], true);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------
-constexpr int kFwdChunk = 32;
+#ifndef PSIG_FWD_CHUNK
+#define PSIG_FWD_CHUNK 64
+#endif
+constexpr int kFwdChunk = PSIG_FWD_CHUNK;
 
-template <int D, int N, int P, int DA, int NT>
-__global__ void __launch_bounds__(NT) sig_forward_tiled(const float *__restrict__ path, float *__restrict__ out,
-                                                        long long L, long long W, const int *__restrict__ windows,
-                                                        int vec_ok)
+template <int D, int N, int P, int DA>
+struct ForwardState {
+    using S = Shape<D, N, P, DA>;
+    float pref[P + 1];
+    float R1[S::n1], R2[at_least_one(S::n2)], R3[at_least_one(S::n3)];
+};
+
+template <int D, int N, int P, int DA>
+__device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const StepOperands<D, DA, P, N - P> &o)
+{
+    constexpr int Q = N - P;
+    if constexpr (Q >= 3) {  // target degree P+3
+        constexpr int k = P + 3;
+        float bb = 1.f;
+#pragma unroll
+        for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
+#pragma unroll
+        for (int a = 0; a < DA; ++a) {
+            const float v1 = fmaf(bb, o.dxa3[a], s.R1[a]);
+#pragma unroll
+            for (int c = 0; c < D; ++c) {
+                const float v2 = fmaf(v1, o.dxf2[c], s.R2[a * D + c]);
+#pragma unroll
+                for (int e = 0; e < D; ++e) s.R3[(a * D + c) * D + e] = fmaf(v2, o.dxf1[e], s.R3[(a * D + c) * D + e]);
+            }
+        }
+    }
+    if constexpr (Q >= 2) {  // target degree P+2
+        constexpr int k = P + 2;
+        float bb = 1.f;
+#pragma unroll
+        for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
+#pragma unroll
+        for (int a = 0; a < DA; ++a) {
+            const float v1 = fmaf(bb, o.dxa2[a], s.R1[a]);
+#pragma unroll
+            for (int c = 0; c < D; ++c) s.R2[a * D + c] = fmaf(v1, o.dxf1[c], s.R2[a * D + c]);
+        }
+    }
+    {  // target degree P+1
+        constexpr int k = P + 1;
+        float bb = 1.f;
+#pragma unroll
+        for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
+#pragma unroll
+        for (int a = 0; a < DA; ++a) s.R1[a] = fmaf(bb, o.dxa1[a], s.R1[a]);
+    }
+    // the shared prefixes, highest first so each reads the previous step's lower values
+#pragma unroll
+    for (int m = P; m >= 1; --m) {
+        float bm = 1.f;
+#pragma unroll
+        for (int j = 1; j <= m - 1; ++j) bm = fmaf(bm, o.xs[j - 1] * recip<float>(m - j + 1), s.pref[j]);
+        s.pref[m] = fmaf(bm, o.xs[m - 1], s.pref[m]);
+    }
+}
+
+template <int D, int N, int P, int DA, int NT, int MINB>
+__global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__restrict__ path, float *__restrict__ out,
+                                                              long long L, long long W,
+                                                              const int *__restrict__ windows, int vec_ok)
 {
     using S = Shape<D, N, P, DA>;
     constexpr int Q = S::Q, PARTS = S::TPU / NT, CH = kFwdChunk;
@@ -141,87 +241,41 @@ __global__ void __launch_bounds__(NT) sig_forward_tiled(const float *__restrict_
     window_of(unit, L, W, windows, b, start, steps);
     const float *x = path + (b * L + start) * D;
 
-    float pref[P + 1];
-    float R1[S::n1], R2[at_least_one(S::n2)], R3[at_least_one(S::n3)];
+    ForwardState<D, N, P, DA> st;
 #pragma unroll
-    for (int j = 0; j <= P; ++j) pref[j] = 0.f;
+    for (int j = 0; j <= P; ++j) st.pref[j] = 0.f;
 #pragma unroll
-    for (int i = 0; i < S::n1; ++i) R1[i] = 0.f;
+    for (int i = 0; i < S::n1; ++i) st.R1[i] = 0.f;
 #pragma unroll
-    for (int i = 0; i < at_least_one(S::n2); ++i) R2[i] = 0.f;
+    for (int i = 0; i < at_least_one(S::n2); ++i) st.R2[i] = 0.f;
 #pragma unroll
-    for (int i = 0; i < at_least_one(S::n3); ++i) R3[i] = 0.f;
+    for (int i = 0; i < at_least_one(S::n3); ++i) st.R3[i] = 0.f;
 
     for (int c0 = 0; c0 < steps; c0 += CH) {
         const int n = min(CH, steps - c0);
         __syncthreads();
         stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
         __syncthreads();
+#if PSIG_FWD_PREFETCH
+        StepOperands<D, DA, P, Q> oa, ob;
+        load_operands<D, DA, P, Q, CH>(oa, s_dx, 0, let, a0);
 #pragma unroll 1
-        for (int t = 0; t < n; ++t) {
-            const float *row = s_dx[0][t];
-            float xs[P];
-#pragma unroll
-            for (int j = 0; j < P; ++j) xs[j] = row[let[j]];
-            float dxf1[D], dxa1[DA];
-            load_run<D>(dxf1, row, true);
-            if constexpr (DA == D) {
-#pragma unroll
-                for (int a = 0; a < DA; ++a) dxa1[a] = dxf1[a];
-            } else {
-                load_run<DA>(dxa1, row + a0, true);
-            }
-
-            if constexpr (Q >= 3) {  // target degree P+3
-                constexpr int k = P + 3;
-                float dxa3[DA], dxf2[D];
-                load_run<DA>(dxa3, s_dx[2][t] + a0, true);
-                load_run<D>(dxf2, s_dx[1][t], true);
-                float bb = 1.f;
-#pragma unroll
-                for (int j = 1; j <= P; ++j) bb = fmaf(bb, xs[j - 1] * recip<float>(k - j + 1), pref[j]);
-#pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    const float v1 = fmaf(bb, dxa3[a], R1[a]);
-#pragma unroll
-                    for (int c = 0; c < D; ++c) {
-                        const float v2 = fmaf(v1, dxf2[c], R2[a * D + c]);
-#pragma unroll
-                        for (int e = 0; e < D; ++e) R3[(a * D + c) * D + e] = fmaf(v2, dxf1[e], R3[(a * D + c) * D + e]);
-                    }
-                }
-            }
-            if constexpr (Q >= 2) {  // target degree P+2
-                constexpr int k = P + 2;
-                float dxa2[DA];
-                load_run<DA>(dxa2, s_dx[1][t] + a0, true);
-                float bb = 1.f;
-#pragma unroll
-                for (int j = 1; j <= P; ++j) bb = fmaf(bb, xs[j - 1] * recip<float>(k - j + 1), pref[j]);
-#pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    const float v1 = fmaf(bb, dxa2[a], R1[a]);
-#pragma unroll
-                    for (int c = 0; c < D; ++c) R2[a * D + c] = fmaf(v1, dxf1[c], R2[a * D + c]);
-                }
-            }
-            {  // target degree P+1
-                constexpr int k = P + 1;
-                float bb = 1.f;
-#pragma unroll
-                for (int j = 1; j <= P; ++j) bb = fmaf(bb, xs[j - 1] * recip<float>(k - j + 1), pref[j]);
-#pragma unroll
-                for (int a = 0; a < DA; ++a) R1[a] = fmaf(bb, dxa1[a], R1[a]);
-            }
-            // the shared prefixes, highest first
-#pragma unroll
-            for (int m = P; m >= 1; --m) {
-                float bm = 1.f;
-#pragma unroll
-                for (int j = 1; j <= m - 1; ++j) bm = fmaf(bm, xs[j - 1] * recip<float>(m - j + 1), pref[j]);
-                pref[m] = fmaf(bm, xs[m - 1], pref[m]);
+        for (int t = 0; t < n; t += 2) {
+            if (t + 1 < n) load_operands<D, DA, P, Q, CH>(ob, s_dx, t + 1, let, a0);
+            forward_step<D, N, P, DA>(st, oa);
+            if (t + 1 < n) {
+                if (t + 2 < n) load_operands<D, DA, P, Q, CH>(oa, s_dx, t + 2, let, a0);
+                forward_step<D, N, P, DA>(st, ob);
             }
         }
+#else
+#pragma unroll 1
+        for (int t = 0; t < n; ++t) {
+            StepOperands<D, DA, P, Q> o;
+            load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
+            forward_step<D, N, P, DA>(st, o);
+        }
+#endif
     }
 
     float *row = out + unit * S::TOTAL;
@@ -229,19 +283,27 @@ __global__ void __launch_bounds__(NT) sig_forward_tiled(const float *__restrict_
 #pragma unroll
     for (int j = 1; j <= P; ++j) {
         const int span = ipow(D, P - j) * S::SPLIT;  // threads sharing the prefix of length j
-        if (tu % span == 0) row[S::dense_off(j) + tu / span] = pref[j];
+        if (tu % span == 0) row[S::dense_off(j) + tu / span] = st.pref[j];
     }
     const long long base1 = (long long)u * D + a0;
-    store_run<S::n1>(row + S::dense_off(P + 1) + base1, R1, vec);
-    if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, R2, vec);
-    if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, R3, vec);
+    store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+    if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
+    if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
 }
 
 // ------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------
 
-// Push the adjoint `adj` of the scalar Horner value at prefix length P of target degree k down
+template <int D, int N, int P, int DA>
+struct BackwardState {
+    using S = Shape<D, N, P, DA>;
+    float pref[P + 1], apref[P + 1];                      // S and partial adjoint at the shared prefixes
+    float RS1[S::n1], RS2[at_least_one(S::n2)];           // S at degrees P+1, P+2 (tracked while below N)
+    float RG1[S::n1], RG2[at_least_one(S::n2)], RG3[at_least_one(S::n3)];  // adjoints at degrees P+1..N
+};
+
+// Push the adjoint `adj` of the scalar Horner value at prefix length P of target degree K down
 // to the root: adds to the partial adjoints of the shared prefixes and to the letter gradients.
 template <int P, int K>
 __device__ __forceinline__ void back_chain(float adj, const float (&bc)[P + 1], const float (&xs)[P],
@@ -250,8 +312,7 @@ __device__ __forceinline__ void back_chain(float adj, const float (&bc)[P + 1], 
 #pragma unroll
     for (int j = P; j >= 1; --j) {
         apref[j] += adj;
-        constexpr float one = 1.f;
-        const float c = one / float(K - j + 1);
+        const float c = 1.f / float(K - j + 1);
         lg[j - 1] = fmaf(adj * c, bc[j - 1], lg[j - 1]);
         adj = adj * (xs[j - 1] * c);
     }
@@ -265,26 +326,163 @@ __device__ __forceinline__ void head_chain(float (&bc)[P + 1], const float (&xs)
     for (int j = 1; j <= P; ++j) bc[j] = fmaf(bc[j - 1], xs[j - 1] * (1.f / float(K - j + 1)), pref[j]);
 }
 
+// One reverse step.  On return gdf[e] / gda[a] / lg[j] hold this thread's share of dL/d(dx_t)
+// for letter e, for letter a0+a and for the prefix letter let[j].
+template <int D, int N, int P, int DA>
+__device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, const StepOperands<D, DA, P, N - P> &o,
+                                              float (&gdf)[D], float (&gda)[DA], float (&lg)[P])
+{
+    constexpr int Q = N - P;
+#pragma unroll
+    for (int e = 0; e < D; ++e) gdf[e] = 0.f;
+#pragma unroll
+    for (int a = 0; a < DA; ++a) gda[a] = 0.f;
+#pragma unroll
+    for (int j = 0; j < P; ++j) lg[j] = 0.f;
+
+    // shared prefixes, bottom-up: roll back, then transpose
+#pragma unroll
+    for (int m = 1; m <= P; ++m) {
+        float bc[P + 1];
+        bc[0] = 1.f;
+#pragma unroll
+        for (int j = 1; j <= m - 1; ++j) bc[j] = fmaf(bc[j - 1], o.xs[j - 1] * (1.f / float(m - j + 1)), s.pref[j]);
+        s.pref[m] = fmaf(-bc[m - 1], o.xs[m - 1], s.pref[m]);
+        const float a = s.apref[m];
+        lg[m - 1] = fmaf(a, bc[m - 1], lg[m - 1]);
+        float adj = a * o.xs[m - 1];
+#pragma unroll
+        for (int j = m - 1; j >= 1; --j) {
+            s.apref[j] += adj;
+            const float c = 1.f / float(m - j + 1);
+            lg[j - 1] = fmaf(adj * c, bc[j - 1], lg[j - 1]);
+            adj = adj * (o.xs[j - 1] * c);
+        }
+    }
+    {  // target degree P+1
+        constexpr int k = P + 1;
+        float bc[P + 1];
+        head_chain<P, k>(bc, o.xs, s.pref);
+        const float bb = bc[P];
+        float adj = 0.f;
+#pragma unroll
+        for (int a = 0; a < DA; ++a) {
+            if constexpr (Q >= 2) s.RS1[a] = fmaf(-bb, o.dxa1[a], s.RS1[a]);
+            adj = fmaf(s.RG1[a], o.dxa1[a], adj);
+            gda[a] = fmaf(s.RG1[a], bb, gda[a]);
+        }
+        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+    }
+    if constexpr (Q >= 2) {  // target degree P+2
+        constexpr int k = P + 2;
+        float bc[P + 1];
+        head_chain<P, k>(bc, o.xs, s.pref);
+        const float bb = bc[P];
+        float adj = 0.f;
+#pragma unroll
+        for (int a = 0; a < DA; ++a) {
+            const float v1 = fmaf(bb, o.dxa2[a], s.RS1[a]);
+            float av = 0.f;
+#pragma unroll
+            for (int c = 0; c < D; ++c) {
+                if constexpr (Q >= 3) s.RS2[a * D + c] = fmaf(-v1, o.dxf1[c], s.RS2[a * D + c]);
+                const float g = s.RG2[a * D + c];
+                av = fmaf(g, o.dxf1[c], av);
+                gdf[c] = fmaf(g, v1, gdf[c]);
+            }
+            s.RG1[a] += av;
+            adj = fmaf(av, o.dxa2[a], adj);
+            gda[a] = fmaf(av * 0.5f, bb, gda[a]);
+        }
+        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+    }
+    if constexpr (Q >= 3) {  // target degree P+3
+        constexpr int k = P + 3;
+        float bc[P + 1];
+        head_chain<P, k>(bc, o.xs, s.pref);
+        const float bb = bc[P];
+        float adj = 0.f;
+#pragma unroll
+        for (int a = 0; a < DA; ++a) {
+            const float v1 = fmaf(bb, o.dxa3[a], s.RS1[a]);
+            float av1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < D; ++c) {
+                const float v2 = fmaf(v1, o.dxf2[c], s.RS2[a * D + c]);
+                float av2 = 0.f;
+#pragma unroll
+                for (int e = 0; e < D; ++e) {
+                    const float g = s.RG3[(a * D + c) * D + e];
+                    av2 = fmaf(g, o.dxf1[e], av2);
+                    gdf[e] = fmaf(g, v2, gdf[e]);
+                }
+                s.RG2[a * D + c] += av2;
+                av1 = fmaf(av2, o.dxf2[c], av1);
+                gdf[c] = fmaf(av2 * 0.5f, v1, gdf[c]);
+            }
+            s.RG1[a] += av1;
+            adj = fmaf(av1, o.dxa3[a], adj);
+            gda[a] = fmaf(av1 * recip<float>(3), bb, gda[a]);
+        }
+        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+    }
+}
+
 template <int D, int N, int P, int DA, int NT, int CHR>
 struct BackwardSmem {
     static constexpr int Q = N - P;
-    static constexpr int kPartRow = NT * D + D;  // one step of per-thread partials (+D floats of padding)
+    // One slot of D floats per thread and step; 4 floats of padding make 128-bit accesses at a
+    // stride of one slot fall into distinct banks.
+    static constexpr int kSlot = D + 4;
+    static constexpr int kPartRow = NT * kSlot;
     static constexpr int kFloats = Q * CHR * D + CHR * kPartRow + (CHR + 1) * D;
     static constexpr size_t kBytes = sizeof(float) * kFloats;
+    // Block-wide sum of the partials: each group of kSlices adjacent lanes produces one float4
+    // (4 letters of one step); used when the shape allows it, otherwise a scalar loop.
+    static constexpr int kQuads = (D % 4 == 0) ? CHR * D / 4 : 1;
+    static constexpr int kSlices = NT / kQuads;
+#ifndef PSIG_VEC_REDUCE
+#define PSIG_VEC_REDUCE 1
+#endif
+    static constexpr bool kVecReduce = PSIG_VEC_REDUCE && (D % 4 == 0) && (NT % kQuads == 0) && kSlices >= 1 && kSlices <= 32 &&
+                                       (kSlices & (kSlices - 1)) == 0;
 };
 
-template <int D, int N, int P, int DA, int NT, int CHR>
-__global__ void __launch_bounds__(NT) sig_backward_tiled(const float *__restrict__ path,
-                                                         const float *__restrict__ sig,
-                                                         const float *__restrict__ grad,
-                                                         float *__restrict__ grad_path,
-                                                         float *__restrict__ inc_grad, long long L, long long W,
-                                                         const int *__restrict__ windows, int vec_ok)
+// Publish this thread's share of dL/d(dx_t) into its slot of the step's row of partials.
+template <int D, int DA, int P>
+__device__ __forceinline__ void publish_partials(float *mine, float (&gdf)[D], const float (&gda)[DA],
+                                                 const float (&lg)[P], const int (&let)[P], int a0)
+{
+    if constexpr (DA == D) {
+#pragma unroll
+        for (int e = 0; e < D; ++e) gdf[e] += gda[e];
+    }
+    store_run<D>(mine, gdf, true);
+    if constexpr (DA != D) {
+#pragma unroll
+        for (int a = 0; a < DA; ++a) mine[a0 + a] += gda[a];
+    }
+#pragma unroll
+    for (int j = 0; j < P; ++j) mine[let[j]] += lg[j];
+}
+
+// `accumulate` == 0: the block owns the whole path (no windows, one block per unit) and stores
+// grad_path directly.  `accumulate` == 1: several blocks contribute to the same points
+// (overlapping windows, or a unit split over several blocks); grad_path was zeroed and
+// receives atomic adds.
+template <int D, int N, int P, int DA, int NT, int CHR, int MINB>
+__global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__restrict__ path,
+                                                               const float *__restrict__ sig,
+                                                               const float *__restrict__ grad,
+                                                               float *__restrict__ grad_path, long long L,
+                                                               long long W, const int *__restrict__ windows,
+                                                               int vec_ok, int accumulate)
 {
     using S = Shape<D, N, P, DA>;
     using SM = BackwardSmem<D, N, P, DA, NT, CHR>;
     constexpr int Q = S::Q, PARTS = S::TPU / NT;
     static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
+    static_assert(NT % 4 == 0, "block size must be a multiple of 4");
     extern __shared__ __align__(16) float smem[];
     float (*s_dx)[CHR][D] = reinterpret_cast<float (*)[CHR][D]>(smem);
     float *s_part = smem + Q * CHR * D;
@@ -304,32 +502,27 @@ __global__ void __launch_bounds__(NT) sig_backward_tiled(const float *__restrict
     window_of(unit, L, W, windows, b, start, steps);
     if (steps == 0) return;
     const float *x = path + (b * L + start) * D;
-    // Direct mode: this block owns the whole path, so it writes grad_path itself.
-    const bool direct = (inc_grad == nullptr);
-    float *gx = grad_path + b * L * D;
-    float *gd = direct ? nullptr : inc_grad + (b * (L - 1) + start) * D;
+    float *gx = grad_path + (b * L + start) * D;  // gradient at the first point of the unit
 
     const bool vec = S::kVecLayout && vec_ok;
     const float *srow = sig + unit * S::TOTAL;
     const float *grow = grad + unit * S::TOTAL;
     const long long base1 = (long long)u * D + a0;
 
-    float pref[P + 1], apref[P + 1];
-    pref[0] = 1.f; apref[0] = 0.f;
+    BackwardState<D, N, P, DA> st;
+    st.pref[0] = 1.f; st.apref[0] = 0.f;
 #pragma unroll
     for (int j = 1; j <= P; ++j) {
         const int span = ipow(D, P - j) * S::SPLIT;
         const long long idx = S::dense_off(j) + tu / span;
-        pref[j] = srow[idx];
-        apref[j] = (tu % span == 0) ? grow[idx] : 0.f;
+        st.pref[j] = srow[idx];
+        st.apref[j] = (tu % span == 0) ? grow[idx] : 0.f;
     }
-    float RS1[S::n1], RS2[at_least_one(S::n2)];          // S at degrees P+1, P+2 (when below N)
-    float RG1[S::n1], RG2[at_least_one(S::n2)], RG3[at_least_one(S::n3)];
-    if constexpr (Q >= 2) load_run<S::n1>(RS1, srow + S::dense_off(P + 1) + base1, vec);
-    if constexpr (Q >= 3) load_run<S::n2>(RS2, srow + S::dense_off(P + 2) + base1 * D, vec);
-    load_run<S::n1>(RG1, grow + S::dense_off(P + 1) + base1, vec);
-    if constexpr (Q >= 2) load_run<S::n2>(RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
-    if constexpr (Q >= 3) load_run<S::n3>(RG3, grow + S::dense_off(P + 3) + base1 * D * D, vec);
+    if constexpr (Q >= 2) load_run<S::n1>(st.RS1, srow + S::dense_off(P + 1) + base1, vec);
+    if constexpr (Q >= 3) load_run<S::n2>(st.RS2, srow + S::dense_off(P + 2) + base1 * D, vec);
+    load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+    if constexpr (Q >= 2) load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
+    if constexpr (Q >= 3) load_run<S::n3>(st.RG3, grow + S::dense_off(P + 3) + base1 * D * D, vec);
 
     for (int i = threadIdx.x; i < D; i += NT) s_red[CHR * D + i] = 0.f;
 
@@ -340,201 +533,150 @@ __global__ void __launch_bounds__(NT) sig_backward_tiled(const float *__restrict
         stage_scaled_increments<D, Q, CHR, NT>(x, c0, n, s_dx);
         __syncthreads();
 
+        float gdf[D], gda[DA], lg[P];
+#if PSIG_BWD_PREFETCH
+        StepOperands<D, DA, P, Q> oa, ob;
+        load_operands<D, DA, P, Q, CHR>(oa, s_dx, n - 1, let, a0);
+#pragma unroll 1
+        for (int t = n - 1; t >= 0; t -= 2) {
+            if (t >= 1) load_operands<D, DA, P, Q, CHR>(ob, s_dx, t - 1, let, a0);
+            backward_step<D, N, P, DA>(st, oa, gdf, gda, lg);
+            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
+            if (t >= 1) {
+                if (t >= 2) load_operands<D, DA, P, Q, CHR>(oa, s_dx, t - 2, let, a0);
+                backward_step<D, N, P, DA>(st, ob, gdf, gda, lg);
+                publish_partials<D, DA, P>(s_part + (t - 1) * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
+            }
+        }
+#else
 #pragma unroll 1
         for (int t = n - 1; t >= 0; --t) {
-            const float *row = s_dx[0][t];
-            float xs[P], lg[P];
-#pragma unroll
-            for (int j = 0; j < P; ++j) { xs[j] = row[let[j]]; lg[j] = 0.f; }
-            float dxf1[D], dxa1[DA], gdf[D], gda[DA];
-            load_run<D>(dxf1, row, true);
-            if constexpr (DA == D) {
-#pragma unroll
-                for (int a = 0; a < DA; ++a) dxa1[a] = dxf1[a];
-            } else {
-                load_run<DA>(dxa1, row + a0, true);
-            }
-#pragma unroll
-            for (int e = 0; e < D; ++e) gdf[e] = 0.f;
-#pragma unroll
-            for (int a = 0; a < DA; ++a) gda[a] = 0.f;
-
-            // shared prefixes, bottom-up: roll back, then transpose
-#pragma unroll
-            for (int m = 1; m <= P; ++m) {
-                float bc[P + 1];
-                bc[0] = 1.f;
-#pragma unroll
-                for (int j = 1; j <= m - 1; ++j) bc[j] = fmaf(bc[j - 1], xs[j - 1] * (1.f / float(m - j + 1)), pref[j]);
-                pref[m] = fmaf(-bc[m - 1], xs[m - 1], pref[m]);
-                const float a = apref[m];
-                lg[m - 1] = fmaf(a, bc[m - 1], lg[m - 1]);
-                float adj = a * xs[m - 1];
-#pragma unroll
-                for (int j = m - 1; j >= 1; --j) {
-                    apref[j] += adj;
-                    const float c = 1.f / float(m - j + 1);
-                    lg[j - 1] = fmaf(adj * c, bc[j - 1], lg[j - 1]);
-                    adj = adj * (xs[j - 1] * c);
-                }
-            }
-            {  // target degree P+1
-                constexpr int k = P + 1;
-                float bc[P + 1];
-                head_chain<P, k>(bc, xs, pref);
-                const float bb = bc[P];
-                float adj = 0.f;
-#pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    if constexpr (Q >= 2) RS1[a] = fmaf(-bb, dxa1[a], RS1[a]);
-                    adj = fmaf(RG1[a], dxa1[a], adj);
-                    gda[a] = fmaf(RG1[a], bb, gda[a]);
-                }
-                back_chain<P, k>(adj, bc, xs, apref, lg);
-            }
-            if constexpr (Q >= 2) {  // target degree P+2
-                constexpr int k = P + 2;
-                float dxa2[DA];
-                load_run<DA>(dxa2, s_dx[1][t] + a0, true);
-                float bc[P + 1];
-                head_chain<P, k>(bc, xs, pref);
-                const float bb = bc[P];
-                float adj = 0.f;
-#pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    const float v1 = fmaf(bb, dxa2[a], RS1[a]);
-                    float av = 0.f;
-#pragma unroll
-                    for (int c = 0; c < D; ++c) {
-                        if constexpr (Q >= 3) RS2[a * D + c] = fmaf(-v1, dxf1[c], RS2[a * D + c]);
-                        const float g = RG2[a * D + c];
-                        av = fmaf(g, dxf1[c], av);
-                        gdf[c] = fmaf(g, v1, gdf[c]);
-                    }
-                    RG1[a] += av;
-                    adj = fmaf(av, dxa2[a], adj);
-                    gda[a] = fmaf(av * 0.5f, bb, gda[a]);
-                }
-                back_chain<P, k>(adj, bc, xs, apref, lg);
-            }
-            if constexpr (Q >= 3) {  // target degree P+3
-                constexpr int k = P + 3;
-                float dxa3[DA], dxf2[D];
-                load_run<DA>(dxa3, s_dx[2][t] + a0, true);
-                load_run<D>(dxf2, s_dx[1][t], true);
-                float bc[P + 1];
-                head_chain<P, k>(bc, xs, pref);
-                const float bb = bc[P];
-                float adj = 0.f;
-#pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    const float v1 = fmaf(bb, dxa3[a], RS1[a]);
-                    float av1 = 0.f;
-#pragma unroll
-                    for (int c = 0; c < D; ++c) {
-                        const float v2 = fmaf(v1, dxf2[c], RS2[a * D + c]);
-                        float av2 = 0.f;
-#pragma unroll
-                        for (int e = 0; e < D; ++e) {
-                            const float g = RG3[(a * D + c) * D + e];
-                            av2 = fmaf(g, dxf1[e], av2);
-                            gdf[e] = fmaf(g, v2, gdf[e]);
-                        }
-                        RG2[a * D + c] += av2;
-                        av1 = fmaf(av2, dxf2[c], av1);
-                        gdf[c] = fmaf(av2 * 0.5f, v1, gdf[c]);
-                    }
-                    RG1[a] += av1;
-                    adj = fmaf(av1, dxa3[a], adj);
-                    gda[a] = fmaf(av1 * recip<float>(3), bb, gda[a]);
-                }
-                back_chain<P, k>(adj, bc, xs, apref, lg);
-            }
-
-            // publish this thread's share of dL/d(dx_t)
-            float *mine = s_part + t * SM::kPartRow + threadIdx.x * D;
-            if constexpr (DA == D) {
-#pragma unroll
-                for (int e = 0; e < D; ++e) gdf[e] += gda[e];
-            }
-            store_run<D>(mine, gdf, true);
-            if constexpr (DA != D) {
-#pragma unroll
-                for (int a = 0; a < DA; ++a) mine[a0 + a] += gda[a];
-            }
-#pragma unroll
-            for (int j = 0; j < P; ++j) mine[let[j]] += lg[j];
+            StepOperands<D, DA, P, Q> o;
+            load_operands<D, DA, P, Q, CHR>(o, s_dx, t, let, a0);
+            backward_step<D, N, P, DA>(st, o, gdf, gda, lg);
+            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
         }
+#endif
         __syncthreads();
         // sum the partials of the block: s_red[t][e]
-        for (int o = threadIdx.x; o < n * D; o += NT) {
-            const int t = o / D, e = o - t * D;
-            const float *col = s_part + t * SM::kPartRow + e;
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if constexpr (SM::kVecReduce) {
+            constexpr int SL = SM::kSlices, QPT = D / 4;
+            const int quad = threadIdx.x / SL, slice = threadIdx.x % SL;
+            const int t = quad / QPT, q4 = quad - t * QPT;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < n) {
+                const float *col = s_part + t * SM::kPartRow + 4 * q4;
 #pragma unroll 4
-            for (int i = 0; i < NT; i += 4) {
-                acc0 += col[(i + 0) * D];
-                acc1 += col[(i + 1) * D];
-                acc2 += col[(i + 2) * D];
-                acc3 += col[(i + 3) * D];
+                for (int i = slice; i < NT; i += SL) {
+                    const float4 v = *reinterpret_cast<const float4 *>(col + i * SM::kSlot);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
             }
-            s_red[o] = (acc0 + acc1) + (acc2 + acc3);
+#pragma unroll
+            for (int off = SL / 2; off > 0; off >>= 1) {
+                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+            }
+            if (slice == 0 && t < n) *reinterpret_cast<float4 *>(s_red + t * D + 4 * q4) = acc;
+        } else {
+            for (int o = threadIdx.x; o < n * D; o += NT) {
+                const int t = o / D, e = o - t * D;
+                const float *col = s_part + t * SM::kPartRow + e;
+                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+#pragma unroll 4
+                for (int i = 0; i < NT; i += 4) {
+                    acc0 += col[(i + 0) * SM::kSlot];
+                    acc1 += col[(i + 1) * SM::kSlot];
+                    acc2 += col[(i + 2) * SM::kSlot];
+                    acc3 += col[(i + 3) * SM::kSlot];
+                }
+                s_red[o] = (acc0 + acc1) + (acc2 + acc3);
+            }
         }
         __syncthreads();
-        if (direct) {
-            // grad_path[p] = g[p-1] - g[p]; g[c0+n] is the carry of the chunk processed before
-            for (int o = threadIdx.x; o < n * D; o += NT) {
-                const int t = o / D, e = o - t * D;  // point p = c0 + t + 1
-                const float later = (t + 1 < n) ? s_red[o + D] : s_red[CHR * D + e];
-                gx[(long long)(start + c0 + t + 1) * D + e] = s_red[o] - later;
-            }
-            if (c0 == 0)
-                for (int e = threadIdx.x; e < D; e += NT) gx[(long long)start * D + e] = -s_red[e];
-            __syncthreads();
-            for (int e = threadIdx.x; e < D; e += NT) s_red[CHR * D + e] = s_red[e];
-        } else {
-            for (int o = threadIdx.x; o < n * D; o += NT) atomicAdd(&gd[(long long)c0 * D + o], s_red[o]);
+        // grad at point p (p = c0+t+1) = g[p-1] - g[p]; g[c0+n] is the carry of the later chunk
+        for (int o = threadIdx.x; o < n * D; o += NT) {
+            const int t = o / D, e = o - t * D;
+            const float later = (t + 1 < n) ? s_red[o + D] : s_red[CHR * D + e];
+            const float v = s_red[o] - later;
+            float *dst = gx + (long long)(c0 + t + 1) * D + e;
+            if (accumulate) atomicAdd(dst, v); else *dst = v;
         }
+        if (c0 == 0) {
+            for (int e = threadIdx.x; e < D; e += NT) {
+                if (accumulate) atomicAdd(gx + e, -s_red[e]); else gx[e] = -s_red[e];
+            }
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < D; e += NT) s_red[CHR * D + e] = s_red[e];
         c_hi = c0;
-    }
-}
-
-template <typename T>
-__global__ void increments_to_points_f32(const T *__restrict__ inc_grad, T *__restrict__ path_grad, long long B,
-                                         long long L, int d)
-{
-    const long long total = B * L * d;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const long long b = i / (L * d);
-        const long long r = i - b * L * d;
-        const long long t = r / d;
-        const int a = (int)(r - t * d);
-        const T *g = inc_grad + b * (L - 1) * d + a;
-        const T after = (t < L - 1) ? g[t * d] : T(0);
-        const T before = (t > 0) ? g[(t - 1) * d] : T(0);
-        path_grad[i] = before - after;
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // configurations
 // ------------------------------------------------------------------------------------------
-template <int D_, int N_, int P_, int DAF_, int NTF_, int DAB_, int NTB_, int CHR_>
+template <int D_, int N_, int P_, int DAF_, int NTF_, int MINBF_, int DAB_, int NTB_, int CHR_, int MINBB_>
 struct Config {
     static constexpr int D = D_, N = N_, P = P_;
-    static constexpr int DAF = DAF_, NTF = NTF_;  // forward: first-letter tile, block size
-    static constexpr int DAB = DAB_, NTB = NTB_, CHR = CHR_;  // backward
+    static constexpr int DAF = DAF_, NTF = NTF_, MINBF = MINBF_;            // forward: first-letter tile, block, min blocks/SM
+    static constexpr int DAB = DAB_, NTB = NTB_, CHR = CHR_, MINBB = MINBB_;  // backward
 };
 
-//                   D  N  P  fwd(DA,NT)  bwd(DA,NT,CHR)
-using Cfg_8_4 = Config<8, 4, 2, 8, 64, 8, 64, 8>;
-using Cfg_8_3 = Config<8, 3, 1, 8, 8, 8, 8, 8>;
-using Cfg_16_4 = Config<16, 4, 2, 8, 256, 4, 256, 4>;
-using Cfg_16_3 = Config<16, 3, 1, 8, 32, 4, 64, 8>;
-using Cfg_4_6 = Config<4, 6, 3, 4, 64, 4, 64, 8>;
-using Cfg_4_5 = Config<4, 5, 2, 4, 16, 4, 16, 8>;
-using Cfg_4_4 = Config<4, 4, 2, 4, 16, 4, 16, 8>;
+// Tunables (each overridable with -D for experiments): forward first-letter tile / block size /
+// minimum resident blocks per SM, then the same for backward plus the steps per reduction chunk.
+#ifndef PSIG_84_DAF
+#define PSIG_84_DAF 8
+#endif
+#ifndef PSIG_84_NTF
+#define PSIG_84_NTF 64
+#endif
+#ifndef PSIG_84_MINBF
+#define PSIG_84_MINBF 1
+#endif
+#ifndef PSIG_84_DAB
+#define PSIG_84_DAB 8
+#endif
+#ifndef PSIG_84_NTB
+#define PSIG_84_NTB 64
+#endif
+#ifndef PSIG_84_CHR
+#define PSIG_84_CHR 8
+#endif
+#ifndef PSIG_84_MINBB
+#define PSIG_84_MINBB 8
+#endif
+#ifndef PSIG_164_DAF
+#define PSIG_164_DAF 8
+#endif
+#ifndef PSIG_164_NTF
+#define PSIG_164_NTF 256
+#endif
+#ifndef PSIG_164_MINBF
+#define PSIG_164_MINBF 1
+#endif
+#ifndef PSIG_164_DAB
+#define PSIG_164_DAB 4
+#endif
+#ifndef PSIG_164_NTB
+#define PSIG_164_NTB 256
+#endif
+#ifndef PSIG_164_CHR
+#define PSIG_164_CHR 4
+#endif
+#ifndef PSIG_164_MINBB
+#define PSIG_164_MINBB 2
+#endif
+#define PSIG_CFG_8_4 8, 4, 2, PSIG_84_DAF, PSIG_84_NTF, PSIG_84_MINBF, PSIG_84_DAB, PSIG_84_NTB, PSIG_84_CHR, PSIG_84_MINBB
+#define PSIG_CFG_16_4 16, 4, 2, PSIG_164_DAF, PSIG_164_NTF, PSIG_164_MINBF, PSIG_164_DAB, PSIG_164_NTB, PSIG_164_CHR, PSIG_164_MINBB
+#define PSIG_CFG_16_3 16, 3, 1, 8, 32, 1, 4, 64, 8, 1
+#define PSIG_CFG_4_6 4, 6, 3, 4, 64, 1, 4, 64, 8, 1
+using Cfg_8_4 = Config<PSIG_CFG_8_4>;
+using Cfg_16_4 = Config<PSIG_CFG_16_4>;
+using Cfg_16_3 = Config<PSIG_CFG_16_3>;
+using Cfg_4_6 = Config<PSIG_CFG_4_6>;
 
 template <typename F>
 bool dispatch(int d, int depth, F &&f)
@@ -567,34 +709,17 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
         constexpr int PARTS = S::TPU / C::NTF;
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
-        sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF><<<(unsigned)blocks, C::NTF, 0, stream>>>(
+        sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF><<<(unsigned)blocks, C::NTF, 0, stream>>>(
             path, out, desc.L, W, desc.W > 0 ? desc.windows : nullptr, aligned16(out) ? 1 : 0);
         rc = check_launch();
     });
     return rc;
 }
 
-namespace {
-template <typename C>
-bool backward_needs_scratch(const PsigSigDesc &desc)
-{
-    using S = Shape<C::D, C::N, C::P, C::DAB>;
-    return desc.W > 0 || (S::TPU / C::NTB) > 1;
-}
-}  // namespace
-
-int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc)
-{
-    int64_t bytes = 0;
-    dispatch(desc.d, desc.depth, [&](auto cfg) {
-        using C = decltype(cfg);
-        if (backward_needs_scratch<C>(desc)) bytes = (int64_t)sizeof(float) * desc.B * (desc.L - 1) * desc.d;
-    });
-    return bytes;
-}
+int64_t tiled_sig_backward_workspace(const PsigSigDesc &) { return 0; }
 
 int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *sig, const float *grad,
-                       float *grad_path, void *workspace, cudaStream_t stream)
+                       float *grad_path, void *, cudaStream_t stream)
 {
     const long long W = desc.W > 0 ? desc.W : 1;
     const long long units = desc.B * W;
@@ -606,33 +731,24 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
         constexpr int PARTS = S::TPU / C::NTB;
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
-        const bool scratch = backward_needs_scratch<C>(desc);
-        float *inc_grad = scratch ? static_cast<float *>(workspace) : nullptr;
-        if (scratch) {
-            const size_t bytes = sizeof(float) * (size_t)desc.B * (size_t)(desc.L - 1) * desc.d;
-            if (cudaMemsetAsync(inc_grad, 0, bytes, stream) != cudaSuccess) { rc = PSIG_ERR_CUDA; return; }
+        // Several blocks add into the same points when windows overlap or a unit spans blocks.
+        const bool accumulate = desc.W > 0 || PARTS > 1;
+        if (accumulate) {
+            const size_t bytes = sizeof(float) * (size_t)desc.B * (size_t)desc.L * desc.d;
+            if (cudaMemsetAsync(grad_path, 0, bytes, stream) != cudaSuccess) { rc = PSIG_ERR_CUDA; return; }
         }
-        auto kernel = sig_backward_tiled<C::D, C::N, C::P, C::DAB, C::NTB, C::CHR>;
+        auto kernel = sig_backward_tiled<C::D, C::N, C::P, C::DAB, C::NTB, C::CHR, C::MINBB>;
         if (SM::kBytes > 48 * 1024) {
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes) !=
                 cudaSuccess) { rc = PSIG_ERR_CUDA; return; }
         }
         if (blocks > 0) {
             const bool vec = aligned16(sig) && aligned16(grad);
-            kernel<<<(unsigned)blocks, C::NTB, SM::kBytes, stream>>>(path, sig, grad, grad_path, inc_grad, desc.L, W,
-                                                                      desc.W > 0 ? desc.windows : nullptr, vec ? 1 : 0);
-            if (check_launch() != PSIG_OK) { rc = PSIG_ERR_CUDA; return; }
+            kernel<<<(unsigned)blocks, C::NTB, SM::kBytes, stream>>>(path, sig, grad, grad_path, desc.L, W,
+                                                                      desc.W > 0 ? desc.windows : nullptr,
+                                                                      vec ? 1 : 0, accumulate ? 1 : 0);
         }
-        if (scratch) {
-            const long long total = desc.B * desc.L * desc.d;
-            long long nb = (total + 255) / 256;
-            if (nb > 148 * 32) nb = 148 * 32;
-            increments_to_points_f32<float><<<(unsigned)nb, 256, 0, stream>>>(inc_grad, grad_path, desc.B, desc.L,
-                                                                               desc.d);
-            rc = check_launch();
-        } else {
-            rc = PSIG_OK;
-        }
+        rc = check_launch();
     });
     return rc;
 }

@@ -1,0 +1,179 @@
+"""CPU tests of the host side: projections, module argument handling, fake (meta) operators,
+and that the C-ABI library exports every symbol include/pathsig_b200.h declares."""
+from __future__ import annotations
+
+import ctypes
+import itertools
+import os
+import re
+
+import pytest
+import torch
+
+import pathsig_b200 as ps
+from pathsig_b200 import _load
+from pathsig_b200.projections import lyndon_words, projections
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ---- C ABI ----
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "pathsig_b200.h")).read()
+    declared = set(re.findall(r"\b(psig_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(_load.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert declared == set(_load.EXPORTS), "ctypes table and header disagree"
+
+
+def test_status_strings_and_sizes_without_a_gpu():
+    lib = _load.ensure_loaded()
+    assert lib.psig_abi_version() == _load.ABI_VERSION
+    assert lib.psig_status_string(0) == b"ok"
+    assert b"depth" in lib.psig_status_string(-3)
+    desc = _load.SigDesc()
+    desc.dtype, desc.d, desc.depth, desc.B, desc.L = 0, 8, 4, 2, 10
+    assert lib.psig_sig_size(ctypes.byref(desc)) == 4680
+    desc.depth = 13
+    assert lib.psig_sig_size(ctypes.byref(desc)) == -3
+    desc.depth, desc.L = 4, 1
+    assert lib.psig_sig_size(ctypes.byref(desc)) == -4
+    desc.L, desc.projected = 10, 1
+    for k, s in enumerate([0, 8, 3, 0, 5]):
+        desc.level_sizes[k] = s
+    desc.words = 1 << 20  # any non-null address; nothing is dereferenced by the size query
+    assert lib.psig_sig_size(ctypes.byref(desc)) == 16
+    ldesc = _load.LogDesc()
+    ldesc.dtype, ldesc.d, ldesc.depth, ldesc.rows, ldesc.top_size = 1, 4, 6, 3, 670
+    ldesc.top_words = 1 << 20
+    assert lib.psig_logsig_size(ctypes.byref(ldesc)) == 1364 + 670
+    assert lib.psig_logsig_backward_workspace(ctypes.byref(ldesc)) == 8 * 3 * 2034 * 6
+
+
+# ---- projections ----
+
+def _is_lyndon(w):
+    return all(w < w[i:] + w[:i] for i in range(1, len(w)))
+
+
+@pytest.mark.parametrize("d,n", [(2, 1), (2, 6), (3, 4), (4, 6), (5, 3)])
+def test_lyndon_words_against_brute_force(d, n):
+    want = [w for w in itertools.product(range(d), repeat=n) if _is_lyndon(w)]
+    codes = lyndon_words(d, n)
+    got = []
+    for c in codes:
+        w = []
+        for _ in range(n):
+            w.append(c % d)
+            c //= d
+        got.append(tuple(reversed(w)))
+    assert got == want
+
+
+def test_lyndon_projection_sizes_and_indices():
+    p = projections.lyndon(6, 4, device="cpu")
+    assert p.level_sizes == [0, 4, 6, 20, 60, 204, 670]
+    assert p.sig_size == 964
+    assert p.encoded_words.shape == (960,) and p.encoded_words.dtype == torch.int64
+    idx = p.logsig_indices()
+    assert idx.shape == (964,)
+    assert idx[:4].tolist() == [0, 1, 2, 3]
+    assert idx[-670:].tolist() == list(range(1364, 1364 + 670))
+    q = projections.lyndon(3, 2, full_levels=(2,), device="cpu")
+    assert q.level_sizes == [0, 2, 4, 2]
+
+
+def test_words_projection_rules():
+    p = projections.words([(0,), (1,), (0, 1), (1, 0), (1, 1, 0)], 3, 2, device="cpu")
+    assert p.level_sizes == [0, 2, 2, 1]          # degree 1 is complete -> implicit
+    assert p.encoded_words.tolist() == [1, 2, 6]
+    # a degree given in full is re-ordered to code order and loses its explicit codes
+    p = projections.words([(1, 1), (0, 0), (1, 0), (0, 1)], 2, 2, device="cpu")
+    assert p.level_sizes == [0, 0, 4] and p.encoded_words.numel() == 0
+    # words beyond the depth end the list
+    p = projections.words([(0,), (0, 1), (0, 1, 1), (1,)], 2, 2, device="cpu")
+    assert p.level_sizes == [0, 1, 1]
+    with pytest.raises(ValueError):
+        projections.words([(0, 1), (1,)], 2, 2, device="cpu")          # decreasing length
+    with pytest.raises(ValueError):
+        projections.words([(0, 2)], 2, 2, device="cpu")                 # letter out of range
+    with pytest.raises(ValueError):
+        projections.words([(0,)], 2, 2, full_levels=(1,), device="cpu")  # explicit words at a full degree
+    with pytest.raises(ValueError):
+        projections.words([], 2, 1, device="cpu")                        # path_dim < 2
+    with pytest.raises(ValueError):
+        projections.words([], 13, 2, device="cpu")
+    with pytest.raises(ValueError):
+        projections.words([], 12, 64, device="cpu")                      # letters do not fit 64/12 bits
+    with pytest.raises(ValueError):
+        projections.words([], 2, 2, full_levels=(3,), device="cpu")
+
+
+def test_anisotropic_projection():
+    p = projections.anisotropic([1.0, 2.0], 3.0, 3, 2, device="cpu")
+    # weight(w) = sum of letter weights <= 3: degree1 {0,1}; degree2 {00,01,10}; degree3 {000}
+    assert p.level_sizes == [0, 2, 3, 1]
+    assert p.encoded_words.tolist() == [0, 1, 2, 0]
+    p = projections.anisotropic(torch.tensor([1.0, 5.0]), 2.0, 3, 2, full_levels=(3,), device="cpu")
+    assert p.level_sizes == [0, 1, 1, 8]
+    assert p.encoded_words.tolist() == [0, 0]
+    with pytest.raises(ValueError):
+        projections.anisotropic([5.0, 5.0], 1.0, 2, 2, device="cpu")
+    with pytest.raises(ValueError):
+        projections.anisotropic([1.0], 1.0, 2, 2, device="cpu")
+    with pytest.raises(ValueError):
+        projections.anisotropic([1.0, -1.0], 1.0, 2, 2, device="cpu")
+    with pytest.raises(ValueError):
+        projections.anisotropic([1.0, 1.0], 0.0, 2, 2, device="cpu")
+
+
+# ---- modules and operators (no GPU: meta device and error paths) ----
+
+def test_module_argument_checks_and_buffers():
+    with pytest.raises(ValueError):
+        ps.Signature(depth=0)
+    with pytest.raises(ValueError):
+        ps.LogSignature(depth=13)
+    with pytest.raises(TypeError):
+        ps.Signature(depth=2, windows=torch.zeros(2, 2, dtype=torch.int32))   # not a CUDA tensor
+    with pytest.raises(TypeError):
+        ps.Signature(depth=2, projection=projections.lyndon(2, 2, device="cpu"))
+    m = ps.Signature(depth=3)
+    assert set(dict(m.named_buffers())) == {"_windows", "_encoded_words"}
+    assert m.state_dict() == {}                                               # unused buffers are not persistent
+    lm = ps.LogSignature(depth=3)
+    assert set(dict(lm.named_buffers())) == {"_windows", "_encoded_words", "_top_words", "_indices_from_sig"}
+
+
+def test_fake_operators_give_reference_shapes():
+    x = torch.empty(32, 128, 8, device="meta")
+    ew = torch.empty(0, dtype=torch.int64, device="meta")
+    win = torch.empty((63, 2), dtype=torch.int32, device="meta")
+    nowin = torch.empty((0, 2), dtype=torch.int32, device="meta")
+    sig = ps.ops.compute_signature(x, 4, False, ew, [], False, nowin)
+    assert sig.shape == (32, 4680)
+    assert ps.ops.compute_signature(x, 4, False, ew, [], True, win).shape == (32, 63, 4680)
+    words = torch.empty(200, dtype=torch.int64, device="meta")
+    assert ps.ops.compute_signature(x, 3, True, words, [0, 8, 100, 100], False, nowin).shape == (32, 208)
+    logsig, cache = ps.ops.sig_to_logsig(sig, 4, 8, False, ew, [0, 8, 64, 512, 4096])
+    assert logsig.shape == (32, 4680) and cache.shape == (32, 4 * 4680)
+    assert ps.ops.signature_backward(x, sig, sig, 4, False, ew, [], False, nowin).shape == x.shape
+    assert ps.ops.logsig_backward(sig, cache, sig, 4, False, ew, [0, 8, 64, 512, 4096]).shape == sig.shape
+    with pytest.raises(RuntimeError):
+        ps.ops.compute_signature(torch.empty(2, 1, 3, device="meta"), 2, False, ew, [], False, nowin)
+
+
+def test_cpu_tensors_are_refused():
+    with pytest.raises(NotImplementedError):
+        ps.ops.compute_signature(torch.zeros(2, 4, 3), 2, False, torch.empty(0, dtype=torch.int64), [], False,
+                                 torch.empty((0, 2), dtype=torch.int32))
+
+
+def test_install_as_pathsig_aliases_the_package():
+    ps.install_as_pathsig()
+    import pathsig
+    assert pathsig.Signature is ps.Signature and pathsig.projections is ps.projections
+    assert torch.ops.pathsig.compute_signature is not None
