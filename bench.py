@@ -41,7 +41,11 @@ UNIT = "paths*steps/s"
 
 # DRAM traffic of one launch of the dominant kernel, from ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # sig_backward_tiled at (8,4): 178.9 MB captured at B=128 (profiles/sig_backward_tiled_d8_n4_cfg2_b128.md),
+    # proportional in units -> B=256
+    "cfg2": 357.7e6,
+}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -556,7 +560,7 @@ def run_ours(args):
         "e2e": main["e2e"],
         "gpu_launches": steps * main["kernels_per_step"],
         "roofline": {
-            "bound": "fp32_fma", "kernel": "signature_backward operator (sig_backward_tiled + increments_to_points)",
+            "bound": "fp32_fma", "kernel": "signature_backward operator (cudaMemsetAsync of grad_path + sig_backward_tiled)",
             "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
             "peak_source": "psig_probe_fp32_fma measured in this process (MEASURED_PEAKS.json has no FP32 figure)",
             "flop_per_launch": bwd_flop, "flop_convention": "backward credited 3 x F_fwd FMAs per path*step",
