@@ -128,6 +128,24 @@ int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
 int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,
                          void *grad_sig, void *workspace, int64_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference.  Same result as psig_sig_backward computed by the generic
+ * kernel, for callers that have no scratch memory to pass and may not allocate any: hosts whose
+ * device memory is entirely owned by a pre-sized arena, enqueue-style hooks that are forbidden
+ * to allocate, loops that cannot take the device-wide synchronisation of cudaMalloc/cudaFree.
+ * The B*(L-1)*d-scalar accumulator the kernel needs is a fixed array inside the library; this
+ * call allocates nothing (no cudaMalloc, no cudaFree, no allocating library routine).
+ *   Limit: sizeof(scalar)*B*(L-1)*d <= psig_sig_backward_static_limit() (8 MiB); larger problems
+ *   return PSIG_ERR_TOO_LARGE and must use psig_sig_backward.
+ *   Every device that loads the library holds those 8 MiB until the process exits.
+ *   The first call on each device looks up the array's device address (with that device
+ *   current); make that first call before starting any stream capture.
+ *   All calls on a device share the one array: the needed part is cleared on the stream before
+ *   each use, and two calls whose GPU work overlaps (different streams, or different threads)
+ *   would corrupt each other -- issue them on one stream or order them with events. */
+int psig_sig_backward_static(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
+                             void *grad_path, void *stream);
+int64_t psig_sig_backward_static_limit(void);
+
 /* Measurement aid with no counterpart in the reference: launches `blocks` x 256 threads that each
  * run `iters` x 128 dependent-chain-free FP32 FMAs on registers only, and returns the number of
  * FMAs issued (or a negative PsigStatus).  Timed by the caller, it gives the FP32 FMA peak used

@@ -20,6 +20,8 @@
 // src/pathsig/backward/sig_backward_kernels.cu:256-318 and 347-377).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace psig {
 namespace {
 
@@ -458,3 +460,76 @@ template int generic_sig_backward<double>(const PsigSigDesc &, const LevelTable 
                                           const double *, double *, double *, cudaStream_t);
 
 }  // namespace psig
+
+// ----------------------------------------------------------------------------------------------
+// psig_sig_backward_static: signature backward for callers that cannot hand us scratch memory
+// ----------------------------------------------------------------------------------------------
+// The generic backward kernel needs a zeroed accumulator of B*(L-1)*d scalars for the gradient
+// with respect to the increments.  psig_sig_backward takes it from the caller; some callers have
+// nothing to give: code that runs where a device allocation is off limits (a pre-sized inference
+// arena owns all of the card's memory, an enqueue-style plugin hook that must not allocate, a
+// latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc/cudaFree
+// imply).  For them the accumulator lives in this fixed array inside the library image.  Every
+// device that loads the library carries these bytes until the process exits, which is why the
+// limit is kept small.
+#define PSIG_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[PSIG_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void *g_scratch_address[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the CURRENT device.  The array's name is only a host-side
+// handle; the address a kernel can use has to be asked for, once per device, while that device
+// is current.
+int static_scratch_address(void **out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PSIG_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_address[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return PSIG_ERR_CUDA;
+        g_scratch_address[dev] = ptr;
+    }
+    *out = g_scratch_address[dev];
+    return PSIG_OK;
+}
+}  // namespace
+
+extern "C" int64_t psig_sig_backward_static_limit(void) { return (int64_t)PSIG_STATIC_SCRATCH_BYTES; }
+
+extern "C" int psig_sig_backward_static(const PsigSigDesc *desc, const void *path, const void *sig,
+                                        const void *grad_sig, void *grad_path, void *stream)
+{
+    using namespace psig;
+    if (!desc) return PSIG_ERR_NULL;
+    if (desc->dtype != PSIG_F32 && desc->dtype != PSIG_F64) return PSIG_ERR_DTYPE;
+    if (desc->depth < 1 || desc->depth > kMaxDepth) return PSIG_ERR_DEPTH;
+    if (desc->B < 0 || desc->L < 2 || desc->d < 1 || desc->W < 0) return PSIG_ERR_SHAPE;
+    if (desc->W > 0 && !desc->windows) return PSIG_ERR_NULL;
+    LevelTable lt;
+    int rc = make_level_table(desc->d, desc->depth, desc->projected != 0, desc->level_sizes, desc->words, false, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->B == 0) return PSIG_OK;
+    if (!path || !grad_path || (lt.total > 0 && (!sig || !grad_sig))) return PSIG_ERR_NULL;
+    const size_t scalar = desc->dtype == PSIG_F32 ? 4 : 8;
+    // B*(L-1)*d scalars must fit the fixed array; anything larger has to go through
+    // psig_sig_backward with caller-provided scratch.
+    const double need = (double)scalar * (double)desc->B * (double)(desc->L - 1) * (double)desc->d;
+    if (need > (double)PSIG_STATIC_SCRATCH_BYTES) return PSIG_ERR_TOO_LARGE;
+    void *scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc != PSIG_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // generic_sig_backward clears the part of the scratch it accumulates into before the kernel
+    // runs, so contents left by an earlier call do not matter.
+    if (desc->dtype == PSIG_F32)
+        return generic_sig_backward<float>(*desc, lt, static_cast<const float *>(path),
+                                           static_cast<const float *>(sig), static_cast<const float *>(grad_sig),
+                                           static_cast<float *>(grad_path), static_cast<float *>(scratch), st);
+    return generic_sig_backward<double>(*desc, lt, static_cast<const double *>(path),
+                                        static_cast<const double *>(sig), static_cast<const double *>(grad_sig),
+                                        static_cast<double *>(grad_path), static_cast<double *>(scratch), st);
+}
