@@ -448,20 +448,23 @@ struct BackwardSmem {
                                        (kSlices & (kSlices - 1)) == 0;
 };
 
-// Publish this thread's share of dL/d(dx_t) into its slot of the step's row of partials.
+// Publish this thread's share of dL/d(dx_t) into its slot of the step's row of partials.  The
+// slice for the owned first letters is folded into the full vector in registers; `split` (which
+// slice this thread owns) is uniform over a block whenever the block size divides D^P, so the
+// selection below does not diverge.
 template <int D, int DA, int P>
 __device__ __forceinline__ void publish_partials(float *mine, float (&gdf)[D], const float (&gda)[DA],
-                                                 const float (&lg)[P], const int (&let)[P], int a0)
+                                                 const float (&lg)[P], const int (&let)[P], int split)
 {
-    if constexpr (DA == D) {
+    constexpr int SPLIT = D / DA;
 #pragma unroll
-        for (int e = 0; e < D; ++e) gdf[e] += gda[e];
+    for (int s2 = 0; s2 < SPLIT; ++s2) {
+        if (split == s2) {
+#pragma unroll
+            for (int a = 0; a < DA; ++a) gdf[s2 * DA + a] += gda[a];
+        }
     }
     store_run<D>(mine, gdf, true);
-    if constexpr (DA != D) {
-#pragma unroll
-        for (int a = 0; a < DA; ++a) mine[a0 + a] += gda[a];
-    }
 #pragma unroll
     for (int j = 0; j < P; ++j) mine[let[j]] += lg[j];
 }
@@ -489,9 +492,12 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     float *s_red = s_part + CHR * SM::kPartRow;  // rows 0..CHR-1: reduced dL/d(dx); row CHR: carry
 
     const long long unit = blockIdx.x / PARTS;
+    // slice-major thread order: all prefixes of slice 0, then slice 1, ... (keeps a0 block-uniform)
+    constexpr int PREFIXES = ipow(D, P);
     const int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
-    const int u = tu / S::SPLIT;
-    const int a0 = (tu % S::SPLIT) * DA;
+    const int split = tu / PREFIXES;
+    const int u = tu - split * PREFIXES;
+    const int a0 = split * DA;
     int let[P];
     {
         int c = u;
@@ -513,10 +519,11 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     st.pref[0] = 1.f; st.apref[0] = 0.f;
 #pragma unroll
     for (int j = 1; j <= P; ++j) {
-        const int span = ipow(D, P - j) * S::SPLIT;
-        const long long idx = S::dense_off(j) + tu / span;
+        const int span = ipow(D, P - j);  // prefixes u sharing u[:j]
+        const long long idx = S::dense_off(j) + u / span;
         st.pref[j] = srow[idx];
-        st.apref[j] = (tu % span == 0) ? grow[idx] : 0.f;
+        // the incoming gradient of a shared prefix is seeded in exactly one of its threads
+        st.apref[j] = (split == 0 && u % span == 0) ? grow[idx] : 0.f;
     }
     if constexpr (Q >= 2) load_run<S::n1>(st.RS1, srow + S::dense_off(P + 1) + base1, vec);
     if constexpr (Q >= 3) load_run<S::n2>(st.RS2, srow + S::dense_off(P + 2) + base1 * D, vec);
@@ -541,11 +548,11 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         for (int t = n - 1; t >= 0; t -= 2) {
             if (t >= 1) load_operands<D, DA, P, Q, CHR>(ob, s_dx, t - 1, let, a0);
             backward_step<D, N, P, DA>(st, oa, gdf, gda, lg);
-            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
+            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
             if (t >= 1) {
                 if (t >= 2) load_operands<D, DA, P, Q, CHR>(oa, s_dx, t - 2, let, a0);
                 backward_step<D, N, P, DA>(st, ob, gdf, gda, lg);
-                publish_partials<D, DA, P>(s_part + (t - 1) * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
+                publish_partials<D, DA, P>(s_part + (t - 1) * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
             }
         }
 #else
@@ -554,7 +561,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
             StepOperands<D, DA, P, Q> o;
             load_operands<D, DA, P, Q, CHR>(o, s_dx, t, let, a0);
             backward_step<D, N, P, DA>(st, o, gdf, gda, lg);
-            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, a0);
+            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
         }
 #endif
         __syncthreads();
@@ -652,13 +659,13 @@ struct Config {
 #define PSIG_164_DAF 8
 #endif
 #ifndef PSIG_164_NTF
-#define PSIG_164_NTF 256
+#define PSIG_164_NTF 128
 #endif
 #ifndef PSIG_164_MINBF
 #define PSIG_164_MINBF 1
 #endif
 #ifndef PSIG_164_DAB
-#define PSIG_164_DAB 4
+#define PSIG_164_DAB 8
 #endif
 #ifndef PSIG_164_NTB
 #define PSIG_164_NTB 256
@@ -667,7 +674,7 @@ struct Config {
 #define PSIG_164_CHR 4
 #endif
 #ifndef PSIG_164_MINBB
-#define PSIG_164_MINBB 2
+#define PSIG_164_MINBB 1
 #endif
 #define PSIG_CFG_8_4 8, 4, 2, PSIG_84_DAF, PSIG_84_NTF, PSIG_84_MINBF, PSIG_84_DAB, PSIG_84_NTB, PSIG_84_CHR, PSIG_84_MINBB
 #define PSIG_CFG_16_4 16, 4, 2, PSIG_164_DAF, PSIG_164_NTF, PSIG_164_MINBF, PSIG_164_DAB, PSIG_164_NTB, PSIG_164_CHR, PSIG_164_MINBB
