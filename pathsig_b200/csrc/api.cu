@@ -75,7 +75,7 @@ int log_table(const PsigLogDesc *desc, LevelTable *lt)
 bool use_tiled(const PsigSigDesc *desc, int *rc)
 {
     *rc = PSIG_OK;
-    const bool eligible = desc->dtype == PSIG_F32 && !desc->projected && tiled_supported(desc->d, desc->depth);
+    const bool eligible = tiled_supported(*desc);
     if (desc->algo == PSIG_ALGO_GENERIC) return false;
     if (desc->algo == PSIG_ALGO_TILED && !eligible) { *rc = PSIG_ERR_UNSUPPORTED; return false; }
     return eligible;

@@ -50,8 +50,8 @@ int generic_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const
                             const T *grad_logsig, T *grad_sig, T *grad_cache_ws, cudaStream_t stream);
 
 // Register-tiled dense float32 kernels (tiled_sig.cu).  `supported` tells whether a kernel
-// exists for (d, depth).
-bool tiled_supported(int d, int depth);
+// exists for this description (dense, or dense below a projected top degree).
+bool tiled_supported(const PsigSigDesc &desc);
 int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cudaStream_t stream);
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
 int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *sig, const float *grad,

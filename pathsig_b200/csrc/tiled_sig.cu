@@ -220,10 +220,12 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
 template <int D, int N, int P, int DA, int NT, int MINB>
 __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__restrict__ path, float *__restrict__ out,
                                                               long long L, long long W,
-                                                              const int *__restrict__ windows, int vec_ok)
+                                                              const int *__restrict__ windows, int vec_ok,
+                                                              const long long *__restrict__ top_words, int top_size)
 {
     using S = Shape<D, N, P, DA>;
     constexpr int Q = S::Q, PARTS = S::TPU / NT, CH = kFwdChunk;
+    extern __shared__ __align__(16) float s_top[];  // D^N floats, only when the top degree is projected
     static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
     __shared__ __align__(16) float s_dx[Q][CH][D];
 
@@ -278,7 +280,10 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
 #endif
     }
 
-    float *row = out + unit * S::TOTAL;
+    // Row layout: dense degrees 1..N, or (top_words != nullptr) dense degrees 1..N-1 followed by
+    // the top_size requested words of degree N in the caller's order.
+    const long long width = top_words ? S::dense_off(N) + top_size : S::TOTAL;
+    float *row = out + unit * width;
     const bool vec = S::kVecLayout && vec_ok;
 #pragma unroll
     for (int j = 1; j <= P; ++j) {
@@ -286,9 +291,26 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
         if (tu % span == 0) row[S::dense_off(j) + tu / span] = st.pref[j];
     }
     const long long base1 = (long long)u * D + a0;
-    store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
-    if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
-    if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
+    if (top_words == nullptr) {
+        store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+        if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
+        if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
+    } else {
+        // the block holds the whole unit (checked by the launcher): stage the dense top degree in
+        // shared memory and copy out the requested words
+        if constexpr (Q == 1) {
+            store_run<S::n1>(s_top + base1, st.R1, true);
+        } else if constexpr (Q == 2) {
+            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+            store_run<S::n2>(s_top + base1 * D, st.R2, true);
+        } else {
+            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+            store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
+            store_run<S::n3>(s_top + base1 * D * D, st.R3, true);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < top_size; i += NT) row[S::dense_off(N) + i] = s_top[top_words[i]];
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -479,7 +501,8 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
                                                                const float *__restrict__ grad,
                                                                float *__restrict__ grad_path, long long L,
                                                                long long W, const int *__restrict__ windows,
-                                                               int vec_ok, int accumulate)
+                                                               int vec_ok, int accumulate,
+                                                               const long long *__restrict__ top_words, int top_size)
 {
     using S = Shape<D, N, P, DA>;
     using SM = BackwardSmem<D, N, P, DA, NT, CHR>;
@@ -511,8 +534,9 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     float *gx = grad_path + (b * L + start) * D;  // gradient at the first point of the unit
 
     const bool vec = S::kVecLayout && vec_ok;
-    const float *srow = sig + unit * S::TOTAL;
-    const float *grow = grad + unit * S::TOTAL;
+    const long long width = top_words ? S::dense_off(N) + top_size : S::TOTAL;
+    const float *srow = sig + unit * width;
+    const float *grow = grad + unit * width;
     const long long base1 = (long long)u * D + a0;
 
     BackwardState<D, N, P, DA> st;
@@ -527,9 +551,30 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     }
     if constexpr (Q >= 2) load_run<S::n1>(st.RS1, srow + S::dense_off(P + 1) + base1, vec);
     if constexpr (Q >= 3) load_run<S::n2>(st.RS2, srow + S::dense_off(P + 2) + base1 * D, vec);
-    load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
-    if constexpr (Q >= 2) load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
-    if constexpr (Q >= 3) load_run<S::n3>(st.RG3, grow + S::dense_off(P + 3) + base1 * D * D, vec);
+    if (top_words == nullptr) {
+        load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+        if constexpr (Q >= 2) load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
+        if constexpr (Q >= 3) load_run<S::n3>(st.RG3, grow + S::dense_off(P + 3) + base1 * D * D, vec);
+    } else {
+        // projected top degree: scatter the incoming gradient of the requested words into a dense
+        // image of the degree (zeros elsewhere) in shared memory, then pick up the owned run
+        float *s_top = s_part;  // the partials area is free until the first step
+        for (int i = threadIdx.x; i < ipow(D, N); i += NT) s_top[i] = 0.f;
+        __syncthreads();
+        for (int i = threadIdx.x; i < top_size; i += NT) atomicAdd(&s_top[top_words[i]], grow[S::dense_off(N) + i]);
+        __syncthreads();
+        if constexpr (Q == 1) {
+            load_run<S::n1>(st.RG1, s_top + base1, true);
+        } else if constexpr (Q == 2) {
+            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+            load_run<S::n2>(st.RG2, s_top + base1 * D, true);
+        } else {
+            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+            load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
+            load_run<S::n3>(st.RG3, s_top + base1 * D * D, true);
+        }
+        __syncthreads();
+    }
 
     for (int i = threadIdx.x; i < D; i += NT) s_red[CHR * D + i] = 0.f;
 
@@ -697,11 +742,46 @@ bool dispatch(int d, int depth, F &&f)
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Largest dense top degree (floats) that the projected-top epilogue stages in shared memory.
+constexpr long long kMaxStagedTop = 8192;
+
+// Row layouts the tiled kernels accept: all degrees dense (also when a projection lists every
+// degree as complete), or every degree below the top dense and the top degree an explicit word
+// list (the layout LogSignature asks for).
+enum class RowKind { kUnsupported, kDense, kProjectedTop };
+
+RowKind classify_rows(const PsigSigDesc &desc, long long *top_size)
+{
+    *top_size = 0;
+    if (!desc.projected) return RowKind::kDense;
+    long long d_pow = 1;
+    for (int k = 1; k < desc.depth; ++k) {
+        d_pow *= desc.d;
+        if (desc.level_sizes[k] != d_pow) return RowKind::kUnsupported;
+    }
+    d_pow *= desc.d;
+    const long long top = desc.level_sizes[desc.depth];
+    if (top == d_pow) return RowKind::kDense;
+    if (top < 0 || top > 0x7fffffffLL || d_pow > kMaxStagedTop) return RowKind::kUnsupported;
+    *top_size = top;
+    return RowKind::kProjectedTop;
+}
+
 }  // namespace
 
-bool tiled_supported(int d, int depth)
+bool tiled_supported(const PsigSigDesc &desc)
 {
-    return dispatch(d, depth, [](auto) {});
+    if (desc.dtype != PSIG_F32) return false;
+    bool one_block_per_unit = false;
+    const bool known = dispatch(desc.d, desc.depth, [&](auto cfg) {
+        using C = decltype(cfg);
+        one_block_per_unit = Shape<C::D, C::N, C::P, C::DAF>::TPU == C::NTF &&
+                             Shape<C::D, C::N, C::P, C::DAB>::TPU == C::NTB;
+    });
+    if (!known) return false;
+    long long top_size = 0;
+    const RowKind kind = classify_rows(desc, &top_size);
+    return kind == RowKind::kDense || (kind == RowKind::kProjectedTop && one_block_per_unit);
 }
 
 int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cudaStream_t stream)
@@ -709,6 +789,8 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
     const long long W = desc.W > 0 ? desc.W : 1;
     const long long units = desc.B * W;
     if (units == 0) return PSIG_OK;
+    long long top_size = 0;
+    const bool projected = classify_rows(desc, &top_size) == RowKind::kProjectedTop;
     int rc = PSIG_ERR_UNSUPPORTED;
     dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
@@ -716,8 +798,11 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
         constexpr int PARTS = S::TPU / C::NTF;
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
-        sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF><<<(unsigned)blocks, C::NTF, 0, stream>>>(
-            path, out, desc.L, W, desc.W > 0 ? desc.windows : nullptr, aligned16(out) ? 1 : 0);
+        const long long width = projected ? S::dense_off(C::N) + top_size : S::TOTAL;
+        const size_t smem = projected ? sizeof(float) * (size_t)ipow(C::D, C::N) : 0;
+        sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF><<<(unsigned)blocks, C::NTF, smem, stream>>>(
+            path, out, desc.L, W, desc.W > 0 ? desc.windows : nullptr, (aligned16(out) && width % 4 == 0) ? 1 : 0,
+            projected ? reinterpret_cast<const long long *>(desc.words) : nullptr, (int)top_size);
         rc = check_launch();
     });
     return rc;
@@ -730,6 +815,8 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
 {
     const long long W = desc.W > 0 ? desc.W : 1;
     const long long units = desc.B * W;
+    long long top_size = 0;
+    const bool projected = classify_rows(desc, &top_size) == RowKind::kProjectedTop;
     int rc = PSIG_ERR_UNSUPPORTED;
     dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
@@ -744,16 +831,25 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
             const size_t bytes = sizeof(float) * (size_t)desc.B * (size_t)desc.L * desc.d;
             if (cudaMemsetAsync(grad_path, 0, bytes, stream) != cudaSuccess) { rc = PSIG_ERR_CUDA; return; }
         }
+        // the projected-top prologue stages D^N floats in the partials area
+        size_t smem = SM::kBytes;
+        if (projected) {
+            const size_t need = sizeof(float) * ((size_t)SM::Q * C::CHR * C::D + (size_t)ipow(C::D, C::N));
+            if (need > smem) smem = need;
+        }
         auto kernel = sig_backward_tiled<C::D, C::N, C::P, C::DAB, C::NTB, C::CHR, C::MINBB>;
-        if (SM::kBytes > 48 * 1024) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes) !=
-                cudaSuccess) { rc = PSIG_ERR_CUDA; return; }
+        if (smem > 48 * 1024) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                rc = PSIG_ERR_CUDA; return;
+            }
         }
         if (blocks > 0) {
-            const bool vec = aligned16(sig) && aligned16(grad);
-            kernel<<<(unsigned)blocks, C::NTB, SM::kBytes, stream>>>(path, sig, grad, grad_path, desc.L, W,
-                                                                      desc.W > 0 ? desc.windows : nullptr,
-                                                                      vec ? 1 : 0, accumulate ? 1 : 0);
+            const long long width = projected ? S::dense_off(C::N) + top_size : S::TOTAL;
+            const bool vec = aligned16(sig) && aligned16(grad) && width % 4 == 0;
+            kernel<<<(unsigned)blocks, C::NTB, smem, stream>>>(
+                path, sig, grad, grad_path, desc.L, W, desc.W > 0 ? desc.windows : nullptr, vec ? 1 : 0,
+                accumulate ? 1 : 0, projected ? reinterpret_cast<const long long *>(desc.words) : nullptr,
+                (int)top_size);
         }
         rc = check_launch();
     });

@@ -205,3 +205,33 @@ def test_tiled_unsupported_shape_is_an_error(ps):
             ps.Signature(depth=5)(torch.zeros(1, 4, 3, device=DEV))
     finally:
         ps.ops.set_algorithm("auto")
+
+
+@pytest.mark.parametrize("d,depth", [(4, 6), (8, 4), (16, 3)])
+@pytest.mark.parametrize("windowed", [False, True])
+def test_tiled_projected_top_degree(ps, oracle, d, depth, windowed):
+    """Dense degrees below a projected top degree (the LogSignature layout) on the tiled kernels."""
+    top = util.random_words(37, d, depth, depth, seed=d)
+    proj = ps.projections.words(top, depth, d, full_levels=tuple(range(1, depth)))
+    assert proj.level_sizes[depth] == 37
+    x = util.brownian_path(3, 45, d, seed=3 * d, dtype=torch.float32)
+    win = util.sliding_windows(45, 20, 9) if windowed else None
+    _run_sig(ps, oracle, x, depth, proj=proj, windows=win, algo="tiled")
+    _run_sig(ps, oracle, x, depth, proj=proj, windows=win, algo="generic")
+
+
+def test_lyndon_logsignature_float32_on_tiled_kernels(ps, oracle):
+    d, depth = 4, 6
+    x = util.brownian_path(4, 60, d, seed=99, dtype=torch.float32)
+    mod = ps.LogSignature(depth=depth, projection=ps.projections.lyndon(depth, d))
+    ps.ops.set_algorithm("tiled")
+    try:
+        xg = x.to(DEV).requires_grad_(True)
+        out = mod(xg)
+        g = util.normal_like(out.shape, 7, torch.float32)
+        (out * g.to(DEV)).sum().backward()
+    finally:
+        ps.ops.set_algorithm("auto")
+    want, want_grad = _oracle_logsig(oracle, mod, x.double(), g.double(), None)
+    assert util.rel_error(out, want) < util.TOL[torch.float32]
+    assert util.rel_error(xg.grad, want_grad) < util.TOL[torch.float32]
