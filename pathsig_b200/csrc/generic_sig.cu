@@ -27,6 +27,7 @@ namespace {
 
 constexpr int kBlock = 128;
 constexpr size_t kStageBytes = 24 * 1024;
+constexpr size_t kSlotBytes = 44 * 1024;
 
 struct GenericPlan {
     LevelTable lt;
@@ -34,6 +35,7 @@ struct GenericPlan {
     long long first_block[kMaxDepth + 2];  // first block of each degree inside a unit
     int tiles;                             // letter tiles per dense prefix
     int chunk;                             // steps staged per refill
+    int slot_stride;                       // backward: floats per private gradient slot (0 = shared atomics)
     long long B, L, W;                     // W >= 1
     const int *windows;
 };
@@ -233,18 +235,26 @@ __device__ void level_backward(const GenericPlan &p, long long unit, long long i
     }
 
     // Reverse sweep, chunk by chunk from the end.
+    const bool slots = p.slot_stride > 0;
+    const long long block_first = idx - threadIdx.x;  // item index of thread 0 of this block
+    const int nact = (int)max(0LL, min((long long)kBlock, p.items[K] - block_first));
     const int nchunks = (steps + p.chunk - 1) / p.chunk;
     for (int ci = nchunks - 1; ci >= 0; --ci) {
         const int c0 = ci * p.chunk;
         const int n = min(p.chunk, steps - c0);
         __syncthreads();
         stage_increments(x, d, c0, n, s_dx);
-        for (int i = threadIdx.x; i < n * d; i += kBlock) s_gd[i] = T(0);
+        if (!slots)
+            for (int i = threadIdx.x; i < n * d; i += kBlock) s_gd[i] = T(0);
         __syncthreads();
         if (it.nb > 0) {
             for (int t = n - 1; t >= 0; --t) {
                 const T *dx = s_dx + t * d;
-                T *sg = s_gd + t * d;
+                // where this step's increment gradients go: the block's shared row (atomics), or
+                // this thread's private slot, zeroed first
+                T *sg = slots ? s_gd + ((size_t)t * kBlock + threadIdx.x) * p.slot_stride : s_gd + t * d;
+                if (slots)
+                    for (int a = 0; a < d; ++a) sg[a] = T(0);
                 T xs[K > 1 ? K - 1 : 1], lg[K > 1 ? K - 1 : 1];
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) { xs[j] = dx[let[j]]; lg[j] = T(0); }
@@ -279,7 +289,8 @@ __device__ void level_backward(const GenericPlan &p, long long unit, long long i
                     for (int i = 0; i < TB; ++i) {
                         if (i < it.nb) {
                             adj = fma(g[i], dx[it.b0 + i], adj);
-                            atomicAdd(&sg[it.b0 + i], g[i] * bc[K - 1]);
+                            if (slots) sg[it.b0 + i] += g[i] * bc[K - 1];
+                            else atomicAdd(&sg[it.b0 + i], g[i] * bc[K - 1]);
                         }
                     }
 #pragma unroll
@@ -291,12 +302,24 @@ __device__ void level_backward(const GenericPlan &p, long long unit, long long i
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < K - 1; ++j) atomicAdd(&sg[let[j]], lg[j]);
+                for (int j = 0; j < K - 1; ++j) {
+                    if (slots) sg[let[j]] += lg[j];
+                    else atomicAdd(&sg[let[j]], lg[j]);
+                }
             }
         }
         __syncthreads();
         for (int i = threadIdx.x; i < n * d; i += kBlock) {
-            const T v = s_gd[i];
+            T v;
+            if (slots) {
+                // fixed-order sum over the active threads' slots
+                const int t = i / d, a = i - t * d;
+                const T *col = s_gd + (size_t)t * kBlock * p.slot_stride + a;
+                v = T(0);
+                for (int thr = 0; thr < nact; ++thr) v += col[(size_t)thr * p.slot_stride];
+            } else {
+                v = s_gd[i];
+            }
             if (v != T(0)) atomicAdd(&gd[(long long)c0 * d + i], v);
         }
     }
@@ -404,6 +427,19 @@ int make_plan(const PsigSigDesc &desc, const LevelTable &lt, int buffers, Generi
     if (chunk < 1) chunk = 1;
     if (chunk > 64) chunk = 64;
     p.chunk = (int)chunk;
+    p.slot_stride = 0;
+    if (buffers == 2) {
+        // Backward with few channels: float atomics on a handful of shared addresses serialise, so
+        // every thread gets a private slot of d scalars per step instead (odd stride: no bank
+        // conflicts in the column sums).  Needs at least two steps per chunk to be worth it.
+        const int stride = lt.d | 1;
+        const size_t slot_step = sizeof(T) * ((size_t)lt.d + (size_t)kBlock * stride);
+        const long long slot_chunk = (long long)(kSlotBytes / slot_step);
+        if (slot_chunk >= 2) {
+            p.slot_stride = stride;
+            p.chunk = (int)(slot_chunk > 32 ? 32 : slot_chunk);
+        }
+    }
     return PSIG_OK;
 }
 
@@ -440,7 +476,9 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
     if (cudaMemsetAsync(inc_grad_ws, 0, inc_bytes, stream) != cudaSuccess) return PSIG_ERR_CUDA;
     if (units > 0 && blocks > 0) {
         const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
-        const size_t smem = 2 * sizeof(T) * (size_t)plan.chunk * lt.d;
+        const size_t smem = plan.slot_stride > 0
+                                ? sizeof(T) * (size_t)plan.chunk * ((size_t)lt.d + (size_t)kBlock * plan.slot_stride)
+                                : 2 * sizeof(T) * (size_t)plan.chunk * lt.d;
         sig_backward_generic<T, TB><<<grid, kBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
     }
