@@ -576,7 +576,23 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
 
 
+def _claim_stdout():
+    """Keep stdout for the JSON line only: libraries (NCCL prints its version banner there) are
+    sent to stderr, and the returned file object writes to the real stdout."""
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    global print
+    real_stdout = _claim_stdout()
+    _print = print
+
+    def print(*a, **k):  # noqa: A001  (every print of this module goes to the real stdout)
+        k.setdefault("file", real_stdout)
+        _print(*a, **k)
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -25,12 +25,7 @@
 // global atomics every step (src/pathsig/backward/sig_backward_kernels.cu:204-318).
 #include "common.cuh"
 
-#ifndef PSIG_FWD_PREFETCH
-#define PSIG_FWD_PREFETCH 0
-#endif
-#ifndef PSIG_BWD_PREFETCH
-#define PSIG_BWD_PREFETCH 0
-#endif
+#include <cstdint>
 
 namespace psig {
 namespace {
@@ -113,6 +108,80 @@ __device__ __forceinline__ void stage_scaled_increments(const float *__restrict_
     const float *lo = x + (long long)c0 * D;
     for (int i = threadIdx.x; i < n * D; i += NT) {
         const float v = lo[i + D] - lo[i];
+        (&s_dx[0][0][0])[i] = v;
+        if constexpr (Q >= 2) (&s_dx[1][0][0])[i] = v * 0.5f;
+        if constexpr (Q >= 3) (&s_dx[2][0][0])[i] = v * recip<float>(3);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Asynchronous staging of raw path points: bulk copies issued by one thread (cp.async.bulk, the
+// TMA engine's untiled form) that land in this block's shared memory and signal an mbarrier.
+// Two buffers, so the copy of the next chunk runs under the arithmetic of the current one.
+// Every wait is bounded; if a copy has not landed in time the block reads the same bytes with
+// plain loads (harmless if the copy lands later: same data) and counts the event.
+// ------------------------------------------------------------------------------------------
+__device__ unsigned int g_bulk_copy_timeouts = 0;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes, unsigned long long *bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+constexpr int kBulkWaitPolls = 1 << 20;
+
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, uint32_t parity)
+{
+    for (int i = 0; i < kBulkWaitPolls; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+template <int D, int MAXPTS>
+struct PointPipe {
+    float raw[2][MAXPTS * D];
+    unsigned long long bar[2];
+    int failed;  // set (and never cleared) by any thread whose bounded wait ran out
+};
+
+// Thread 0 only.  Copies `npts` points (npts * D floats, a multiple of 16 bytes) starting at src.
+template <int D, int MAXPTS>
+__device__ __forceinline__ void pipe_issue(PointPipe<D, MAXPTS> &pp, int slot, const float *src, int npts)
+{
+    fence_proxy_async();  // earlier generic-proxy reads of this buffer are ordered before the copy
+    bulk_copy_g2s(pp.raw[slot], src, (uint32_t)(npts * D * sizeof(float)), &pp.bar[slot]);
+}
+
+// s_dx tables from staged points: raw[t*D + a], t = 0..n.
+template <int D, int Q, int CH, int NT>
+__device__ __forceinline__ void scaled_increments_from_points(const float *raw, int n, float (*s_dx)[CH][D])
+{
+    for (int i = threadIdx.x; i < n * D; i += NT) {
+        const float v = raw[i + D] - raw[i];
         (&s_dx[0][0][0])[i] = v;
         if constexpr (Q >= 2) (&s_dx[1][0][0])[i] = v * 0.5f;
         if constexpr (Q >= 3) (&s_dx[2][0][0])[i] = v * recip<float>(3);
@@ -217,7 +286,9 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
     }
 }
 
-template <int D, int N, int P, int DA, int NT, int MINB>
+// PROJ: the top degree is a word list (rows are dense below it).  BULK: stage points with bulk
+// copies (needs 16-byte aligned path rows); otherwise plain loads.
+template <int D, int N, int P, int DA, int NT, int MINB, bool PROJ, bool BULK>
 __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__restrict__ path, float *__restrict__ out,
                                                               long long L, long long W,
                                                               const int *__restrict__ windows, int vec_ok,
@@ -228,6 +299,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     extern __shared__ __align__(16) float s_top[];  // D^N floats, only when the top degree is projected
     static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
     __shared__ __align__(16) float s_dx[Q][CH][D];
+    __shared__ __align__(16) PointPipe<D, BULK ? CH + 1 : 1> s_pipe;  // one float per buffer when unused
 
     const long long unit = blockIdx.x / PARTS;
     const int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
@@ -253,36 +325,76 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
 #pragma unroll
     for (int i = 0; i < at_least_one(S::n3); ++i) st.R3[i] = 0.f;
 
-    for (int c0 = 0; c0 < steps; c0 += CH) {
-        const int n = min(CH, steps - c0);
-        __syncthreads();
-        stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
-        __syncthreads();
-#if PSIG_FWD_PREFETCH
-        StepOperands<D, DA, P, Q> oa, ob;
-        load_operands<D, DA, P, Q, CH>(oa, s_dx, 0, let, a0);
+    if constexpr (!BULK) {
+        for (int c0 = 0; c0 < steps; c0 += CH) {
+            const int n = min(CH, steps - c0);
+            __syncthreads();
+            stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+            __syncthreads();
 #pragma unroll 1
-        for (int t = 0; t < n; t += 2) {
-            if (t + 1 < n) load_operands<D, DA, P, Q, CH>(ob, s_dx, t + 1, let, a0);
-            forward_step<D, N, P, DA>(st, oa);
-            if (t + 1 < n) {
-                if (t + 2 < n) load_operands<D, DA, P, Q, CH>(oa, s_dx, t + 2, let, a0);
-                forward_step<D, N, P, DA>(st, ob);
+            for (int t = 0; t < n; ++t) {
+                StepOperands<D, DA, P, Q> o;
+                load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
+                forward_step<D, N, P, DA>(st, o);
             }
         }
-#else
-#pragma unroll 1
-        for (int t = 0; t < n; ++t) {
-            StepOperands<D, DA, P, Q> o;
-            load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
-            forward_step<D, N, P, DA>(st, o);
+    } else {
+        // Points of chunk ci: [ci*CH, ci*CH + n] -> n+1 points; the copy of chunk ci+1 is in
+        // flight while chunk ci computes.
+        const int nchunks = (steps + CH - 1) / CH;
+        bool bulk = true;
+        if (nchunks > 0) {
+            if (threadIdx.x == 0) {
+                mbar_init(&s_pipe.bar[0], 1);
+                mbar_init(&s_pipe.bar[1], 1);
+                s_pipe.failed = 0;
+                fence_mbar_init();
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) pipe_issue(s_pipe, 0, x, min(CH, steps) + 1);
         }
-#endif
+        int issued = 1;  // chunks whose copy has been issued (meaningful in thread 0 only)
+        for (int ci = 0; ci < nchunks; ++ci) {
+            const int c0 = ci * CH;
+            const int n = min(CH, steps - c0);
+            if (bulk) {
+                if (threadIdx.x == 0 && ci + 1 < nchunks) {
+                    pipe_issue(s_pipe, (ci + 1) & 1, x + (long long)(c0 + CH) * D, min(CH, steps - c0 - CH) + 1);
+                    issued = ci + 2;
+                }
+                if (!mbar_wait_bounded(&s_pipe.bar[ci & 1], (uint32_t)((ci >> 1) & 1))) s_pipe.failed = 1;
+                scaled_increments_from_points<D, Q, CH, NT>(s_pipe.raw[ci & 1], n, s_dx);
+            } else {
+                stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+            }
+            __syncthreads();
+            if (bulk && s_pipe.failed) {
+                // a copy missed its deadline (never seen in practice): count it, read this and all
+                // later chunks with plain loads instead
+                if (threadIdx.x == 0) atomicAdd(&g_bulk_copy_timeouts, 1u);
+                bulk = false;
+                stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+                __syncthreads();
+            }
+#pragma unroll 1
+            for (int t = 0; t < n; ++t) {
+                StepOperands<D, DA, P, Q> o;
+                load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
+                forward_step<D, N, P, DA>(st, o);
+            }
+            __syncthreads();  // tables (and the staged points they came from) are free again
+        }
+        if (threadIdx.x == 0 && nchunks > 0 && s_pipe.failed) {
+            // do not leave the block while one of its copies may still be in flight: one more
+            // bounded wait on the last phase issued into each buffer
+            for (int c = max(0, issued - 2); c < issued; ++c)
+                mbar_wait_bounded(&s_pipe.bar[c & 1], (uint32_t)((c >> 1) & 1));
+        }
     }
 
-    // Row layout: dense degrees 1..N, or (top_words != nullptr) dense degrees 1..N-1 followed by
+    // Row layout: dense degrees 1..N, or (PROJ) dense degrees 1..N-1 followed by
     // the top_size requested words of degree N in the caller's order.
-    const long long width = top_words ? S::dense_off(N) + top_size : S::TOTAL;
+    const long long width = PROJ ? S::dense_off(N) + top_size : S::TOTAL;
     float *row = out + unit * width;
     const bool vec = S::kVecLayout && vec_ok;
 #pragma unroll
@@ -291,7 +403,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
         if (tu % span == 0) row[S::dense_off(j) + tu / span] = st.pref[j];
     }
     const long long base1 = (long long)u * D + a0;
-    if (top_words == nullptr) {
+    if constexpr (!PROJ) {
         store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
         if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
         if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
@@ -586,21 +698,6 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         __syncthreads();
 
         float gdf[D], gda[DA], lg[P];
-#if PSIG_BWD_PREFETCH
-        StepOperands<D, DA, P, Q> oa, ob;
-        load_operands<D, DA, P, Q, CHR>(oa, s_dx, n - 1, let, a0);
-#pragma unroll 1
-        for (int t = n - 1; t >= 0; t -= 2) {
-            if (t >= 1) load_operands<D, DA, P, Q, CHR>(ob, s_dx, t - 1, let, a0);
-            backward_step<D, N, P, DA>(st, oa, gdf, gda, lg);
-            publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
-            if (t >= 1) {
-                if (t >= 2) load_operands<D, DA, P, Q, CHR>(oa, s_dx, t - 2, let, a0);
-                backward_step<D, N, P, DA>(st, ob, gdf, gda, lg);
-                publish_partials<D, DA, P>(s_part + (t - 1) * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
-            }
-        }
-#else
 #pragma unroll 1
         for (int t = n - 1; t >= 0; --t) {
             StepOperands<D, DA, P, Q> o;
@@ -608,7 +705,6 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
             backward_step<D, N, P, DA>(st, o, gdf, gda, lg);
             publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
         }
-#endif
         __syncthreads();
         // sum the partials of the block: s_red[t][e]
         if constexpr (SM::kVecReduce) {
@@ -740,6 +836,11 @@ bool dispatch(int d, int depth, F &&f)
     return false;
 }
 
+#ifndef PSIG_BULK_COPIES
+#define PSIG_BULK_COPIES 1
+#endif
+constexpr bool kUseBulkCopies = PSIG_BULK_COPIES != 0;
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Largest dense top degree (floats) that the projected-top epilogue stages in shared memory.
@@ -800,9 +901,22 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
         const long long width = projected ? S::dense_off(C::N) + top_size : S::TOTAL;
         const size_t smem = projected ? sizeof(float) * (size_t)ipow(C::D, C::N) : 0;
-        sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF><<<(unsigned)blocks, C::NTF, smem, stream>>>(
-            path, out, desc.L, W, desc.W > 0 ? desc.windows : nullptr, (aligned16(out) && width % 4 == 0) ? 1 : 0,
-            projected ? reinterpret_cast<const long long *>(desc.words) : nullptr, (int)top_size);
+        const int vec = (aligned16(out) && width % 4 == 0) ? 1 : 0;
+        const int *win = desc.W > 0 ? desc.windows : nullptr;
+        const long long *words = projected ? reinterpret_cast<const long long *>(desc.words) : nullptr;
+        // Bulk (TMA) staging pays off when a unit has several chunks, so that the next chunk's copy
+        // overlaps the current chunk's arithmetic; short units (one chunk) are faster with plain loads.
+        const bool bulk = kUseBulkCopies && aligned16(path) && desc.W == 0 && desc.L - 1 > kFwdChunk;
+        auto launch = [&](auto kernel) {
+            kernel<<<(unsigned)blocks, C::NTF, smem, stream>>>(path, out, desc.L, W, win, vec, words, (int)top_size);
+        };
+        if (projected) {
+            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, true, true>);
+            else launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, true, false>);
+        } else {
+            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, false, true>);
+            else launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, false, false>);
+        }
         rc = check_launch();
     });
     return rc;
