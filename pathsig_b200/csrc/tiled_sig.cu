@@ -86,6 +86,13 @@ __device__ __forceinline__ void store_run(float *dst, const float (&src)[LEN], b
     for (int i = 0; i < LEN; ++i) dst[i] = src[i];
 }
 
+// Block-wide barrier; a block of one warp only needs warp convergence plus memory ordering.
+template <int NT>
+__device__ __forceinline__ void block_sync()
+{
+    if constexpr (NT <= 32) __syncwarp(); else __syncthreads();
+}
+
 __device__ __forceinline__ void window_of(long long unit, long long L, long long W, const int *windows,
                                           long long &b, int &start, int &steps)
 {
@@ -328,9 +335,9 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     if constexpr (!BULK) {
         for (int c0 = 0; c0 < steps; c0 += CH) {
             const int n = min(CH, steps - c0);
-            __syncthreads();
+            block_sync<NT>();
             stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
-            __syncthreads();
+            block_sync<NT>();
 #pragma unroll 1
             for (int t = 0; t < n; ++t) {
                 StepOperands<D, DA, P, Q> o;
@@ -350,7 +357,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
                 s_pipe.failed = 0;
                 fence_mbar_init();
             }
-            __syncthreads();
+            block_sync<NT>();
             if (threadIdx.x == 0) pipe_issue(s_pipe, 0, x, min(CH, steps) + 1);
         }
         int issued = 1;  // chunks whose copy has been issued (meaningful in thread 0 only)
@@ -367,14 +374,14 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
             } else {
                 stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
             }
-            __syncthreads();
+            block_sync<NT>();
             if (bulk && s_pipe.failed) {
                 // a copy missed its deadline (never seen in practice): count it, read this and all
                 // later chunks with plain loads instead
                 if (threadIdx.x == 0) atomicAdd(&g_bulk_copy_timeouts, 1u);
                 bulk = false;
                 stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
-                __syncthreads();
+                block_sync<NT>();
             }
 #pragma unroll 1
             for (int t = 0; t < n; ++t) {
@@ -382,7 +389,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
                 load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
                 forward_step<D, N, P, DA>(st, o);
             }
-            __syncthreads();  // tables (and the staged points they came from) are free again
+            block_sync<NT>();  // tables (and the staged points they came from) are free again
         }
         if (threadIdx.x == 0 && nchunks > 0 && s_pipe.failed) {
             // do not leave the block while one of its copies may still be in flight: one more
@@ -420,7 +427,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
             store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
             store_run<S::n3>(s_top + base1 * D * D, st.R3, true);
         }
-        __syncthreads();
+        block_sync<NT>();
         for (int i = threadIdx.x; i < top_size; i += NT) row[S::dense_off(N) + i] = s_top[top_words[i]];
     }
 }
@@ -672,9 +679,9 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         // image of the degree (zeros elsewhere) in shared memory, then pick up the owned run
         float *s_top = s_part;  // the partials area is free until the first step
         for (int i = threadIdx.x; i < ipow(D, N); i += NT) s_top[i] = 0.f;
-        __syncthreads();
+        block_sync<NT>();
         for (int i = threadIdx.x; i < top_size; i += NT) atomicAdd(&s_top[top_words[i]], grow[S::dense_off(N) + i]);
-        __syncthreads();
+        block_sync<NT>();
         if constexpr (Q == 1) {
             load_run<S::n1>(st.RG1, s_top + base1, true);
         } else if constexpr (Q == 2) {
@@ -685,7 +692,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
             load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
             load_run<S::n3>(st.RG3, s_top + base1 * D * D, true);
         }
-        __syncthreads();
+        block_sync<NT>();
     }
 
     for (int i = threadIdx.x; i < D; i += NT) s_red[CHR * D + i] = 0.f;
@@ -693,9 +700,9 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     for (int c_hi = steps; c_hi > 0;) {
         const int n = min(CHR, c_hi);
         const int c0 = c_hi - n;
-        __syncthreads();
+        block_sync<NT>();
         stage_scaled_increments<D, Q, CHR, NT>(x, c0, n, s_dx);
-        __syncthreads();
+        block_sync<NT>();
 
         float gdf[D], gda[DA], lg[P];
 #pragma unroll 1
@@ -705,7 +712,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
             backward_step<D, N, P, DA>(st, o, gdf, gda, lg);
             publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
         }
-        __syncthreads();
+        block_sync<NT>();
         // sum the partials of the block: s_red[t][e]
         if constexpr (SM::kVecReduce) {
             constexpr int SL = SM::kSlices, QPT = D / 4;
@@ -743,7 +750,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
                 s_red[o] = (acc0 + acc1) + (acc2 + acc3);
             }
         }
-        __syncthreads();
+        block_sync<NT>();
         // grad at point p (p = c0+t+1) = g[p-1] - g[p]; g[c0+n] is the carry of the later chunk
         for (int o = threadIdx.x; o < n * D; o += NT) {
             const int t = o / D, e = o - t * D;
@@ -757,7 +764,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
                 if (accumulate) atomicAdd(gx + e, -s_red[e]); else gx[e] = -s_red[e];
             }
         }
-        __syncthreads();
+        block_sync<NT>();
         for (int e = threadIdx.x; e < D; e += NT) s_red[CHR * D + e] = s_red[e];
         c_hi = c0;
     }
@@ -809,10 +816,10 @@ struct Config {
 #define PSIG_164_DAB 8
 #endif
 #ifndef PSIG_164_NTB
-#define PSIG_164_NTB 256
+#define PSIG_164_NTB 32
 #endif
 #ifndef PSIG_164_CHR
-#define PSIG_164_CHR 4
+#define PSIG_164_CHR 8
 #endif
 #ifndef PSIG_164_MINBB
 #define PSIG_164_MINBB 1

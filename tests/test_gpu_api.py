@@ -1,0 +1,174 @@
+"""API-level behaviour on the GPU: the self-consistency properties the reference's own test-suite
+checks (tests/test_windows.py and tests/test_projections.py of the reference), restated for this
+package: windowed == per-slice, projected == columns of the full result, gradients of overlapping
+windows add up, float64 gradcheck, shapes, buffers and operator registration checks."""
+from __future__ import annotations
+
+import itertools
+
+import pytest
+import torch
+
+from . import util
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ps():
+    import pathsig_b200
+    return pathsig_b200
+
+
+def _path(B, L, d, seed=42, dtype=torch.float64):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(B, L, d, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+
+
+def _full_columns(proj):
+    d, cols, off, used = proj.path_dim, [], 0, 0
+    codes = proj.encoded_words.tolist()
+    for n in range(1, proj.depth + 1):
+        size = proj.level_sizes[n]
+        if size == d ** n:
+            cols.extend(range(off, off + d ** n))
+        elif size > 0:
+            cols.extend(off + c for c in codes[used: used + size])
+            used += size
+        off += d ** n
+    return torch.tensor(cols, dtype=torch.int64, device=DEV)
+
+
+@pytest.mark.parametrize("kind", ["sig", "logsig"])
+@pytest.mark.parametrize("depth,d", [(2, 2), (3, 3), (4, 4), (4, 2)])
+def test_windowed_equals_per_slice(ps, kind, depth, d):
+    x = _path(3, 50, d)
+    win = util.sliding_windows(50, 15, 5, device=DEV)
+    cls = ps.Signature if kind == "sig" else ps.LogSignature
+    windowed = cls(depth=depth, windows=win)(x)
+    plain = cls(depth=depth)
+    assert windowed.shape[:2] == (3, win.shape[0])
+    for w, (s, e) in enumerate(win.tolist()):
+        torch.testing.assert_close(windowed[:, w], plain(x[:, s:e]), atol=1e-10, rtol=1e-10)
+
+
+def test_window_edge_patterns(ps):
+    x = _path(2, 30, 3)
+    sig = ps.Signature(depth=3)
+    for win in ([[0, 30]], [[0, 2], [28, 30]], [[0, 10], [10, 20], [20, 30]], [[5, 25], [0, 30], [7, 9]]):
+        w = torch.tensor(win, dtype=torch.int64, device=DEV)  # int64 windows are accepted
+        out = ps.Signature(depth=3, windows=w)(x)
+        for i, (s, e) in enumerate(win):
+            torch.testing.assert_close(out[:, i], sig(x[:, s:e]), atol=1e-10, rtol=1e-10)
+
+
+def test_overlapping_window_gradients_add_up(ps):
+    x = _path(2, 24, 3)
+    win = torch.tensor([[0, 12], [6, 18], [10, 24], [3, 5]], dtype=torch.int32, device=DEV)
+    xa = x.clone().requires_grad_(True)
+    out = ps.Signature(depth=3, windows=win)(xa)
+    g = torch.randn_like(out)
+    (out * g).sum().backward()
+    expect = torch.zeros_like(x)
+    for i, (s, e) in enumerate(win.tolist()):
+        xi = x[:, s:e].clone().requires_grad_(True)
+        (ps.Signature(depth=3)(xi) * g[:, i]).sum().backward()
+        expect[:, s:e] += xi.grad
+    torch.testing.assert_close(xa.grad, expect, atol=1e-10, rtol=1e-10)
+
+
+@pytest.mark.parametrize("make", [
+    lambda P: P.lyndon(4, 3),
+    lambda P: P.lyndon(3, 4, full_levels=(2,)),
+    lambda P: P.words([(0,), (2,), (1, 1), (0, 2), (2, 1, 0), (1, 0, 0, 2)], 4, 3),
+    lambda P: P.words([(0, 1), (1, 1, 0)], 3, 2, full_levels=(1,)),
+    lambda P: P.anisotropic([1.0, 2.0, 1.5], 4.5, 4, 3),
+    lambda P: P.anisotropic([1.0, 1.0], 3.0, 3, 2, full_levels=(1, 2)),
+])
+def test_projected_equals_columns_of_full(ps, make):
+    proj = make(ps.projections)
+    x = _path(3, 17, proj.path_dim)
+    cols = _full_columns(proj)
+    xa = x.clone().requires_grad_(True)
+    out = ps.Signature(depth=proj.depth, projection=proj)(xa)
+    assert out.shape == (3, proj.sig_size)
+    xb = x.clone().requires_grad_(True)
+    full = ps.Signature(depth=proj.depth)(xb)
+    torch.testing.assert_close(out, full[:, cols], atol=1e-11, rtol=1e-11)
+    g = torch.randn_like(out)
+    (out * g).sum().backward()
+    (full[:, cols] * g).sum().backward()
+    torch.testing.assert_close(xa.grad, xb.grad, atol=1e-10, rtol=1e-10)
+
+
+def test_lyndon_logsignature_equals_columns_of_full_log(ps):
+    for d, depth in [(2, 5), (3, 4), (4, 3)]:
+        proj = ps.projections.lyndon(depth, d)
+        x = _path(2, 14, d)
+        out = ps.LogSignature(depth=depth, projection=proj)(x)
+        full = ps.LogSignature(depth=depth)(x)
+        torch.testing.assert_close(out, full[:, _full_columns(proj)], atol=1e-11, rtol=1e-11)
+
+
+def test_projection_ignores_extra_channels(ps):
+    """Words over the first d0 letters of a wider path give the signature of the narrower path."""
+    d0, extra, depth = 2, 2, 3
+    x = _path(2, 12, d0 + extra)
+    words = [w for n in range(1, depth + 1) for w in itertools.product(range(d0), repeat=n)]
+    proj = ps.projections.words(words, depth, d0 + extra)
+    out = ps.Signature(depth=depth, projection=proj)(x)
+    narrow = ps.Signature(depth=depth)(x[:, :, :d0].contiguous())
+    torch.testing.assert_close(out, narrow, atol=1e-11, rtol=1e-11)
+
+
+@pytest.mark.parametrize("case", ["sig", "sig_windows", "sig_lyndon", "logsig", "logsig_lyndon_windows"])
+def test_gradcheck_float64(ps, case):
+    d, depth = 2, 3
+    x = (_path(2, 6, d, seed=3) * 0.5).requires_grad_(True)
+    win = torch.tensor([[0, 4], [2, 6]], dtype=torch.int32, device=DEV)
+    mod = {
+        "sig": lambda: ps.Signature(depth=depth),
+        "sig_windows": lambda: ps.Signature(depth=depth, windows=win),
+        "sig_lyndon": lambda: ps.Signature(depth=depth, projection=ps.projections.lyndon(depth, d)),
+        "logsig": lambda: ps.LogSignature(depth=depth),
+        "logsig_lyndon_windows": lambda: ps.LogSignature(depth=depth, projection=ps.projections.lyndon(depth, d),
+                                                         windows=win),
+    }[case]()
+    assert torch.autograd.gradcheck(mod, (x,), eps=1e-6, atol=1e-6, rtol=1e-5, nondet_tol=1e-9)
+
+
+def test_shapes_dtypes_and_state_dict(ps):
+    x32 = _path(4, 9, 3, dtype=torch.float32)
+    assert ps.Signature(depth=3)(x32).dtype == torch.float32
+    assert ps.Signature(depth=3)(x32).shape == (4, 39)
+    assert ps.LogSignature(depth=3)(x32).shape == (4, 39)
+    proj = ps.projections.lyndon(3, 3)
+    assert ps.LogSignature(depth=3, projection=proj)(x32).shape == (4, proj.sig_size)
+    win = util.sliding_windows(9, 4, 2, device=DEV)
+    m = ps.LogSignature(depth=3, projection=proj, windows=win)
+    assert m(x32).shape == (4, win.shape[0], proj.sig_size)
+    sd = m.state_dict()
+    assert set(sd) == {"_windows", "_encoded_words", "_top_words", "_indices_from_sig"}
+    m2 = ps.LogSignature(depth=3, projection=ps.projections.lyndon(3, 3), windows=win.clone())
+    m2.load_state_dict(sd)
+    torch.testing.assert_close(m2(x32), m(x32))
+    assert ps.Signature(depth=2)(x32.double()).dtype == torch.float64
+
+
+def test_operator_registration_checks(ps):
+    """torch.library.opcheck: schema, fake implementation and autograd registration of each operator."""
+    x = _path(2, 7, 2).requires_grad_(True)
+    no_words = torch.empty(0, dtype=torch.int64, device=DEV)
+    no_win = torch.empty((0, 2), dtype=torch.int32, device=DEV)
+    ops = torch.ops.pathsig_b200
+    tests = ("test_schema", "test_faketensor", "test_autograd_registration")
+    torch.library.opcheck(ops.compute_signature.default, (x, 3, False, no_words, [], False, no_win), test_utils=tests)
+    sig = ops.compute_signature(x, 3, False, no_words, [], False, no_win).detach().requires_grad_(True)
+    torch.library.opcheck(ops.sig_to_logsig.default, (sig, 3, 2, False, no_words, [0, 2, 4, 8]), test_utils=tests)
+    g = torch.randn_like(sig)
+    torch.library.opcheck(ops.signature_backward.default, (x.detach(), sig.detach(), g, 3, False, no_words, [],
+                                                            False, no_win), test_utils=("test_schema", "test_faketensor"))
+    _, cache = ops.sig_to_logsig(sig.detach(), 3, 2, False, no_words, [0, 2, 4, 8])
+    torch.library.opcheck(ops.logsig_backward.default, (sig.detach(), cache, g, 3, False, no_words, [0, 2, 4, 8]),
+                          test_utils=("test_schema", "test_faketensor"))
