@@ -31,12 +31,12 @@ constexpr size_t kSlotBytes = 44 * 1024;
 
 struct GenericPlan {
     LevelTable lt;
-    long long items[kMaxDepth + 1];        // thread items per degree
-    long long first_block[kMaxDepth + 2];  // first block of each degree inside a unit
-    int tiles;                             // letter tiles per dense prefix
-    int chunk;                             // steps staged per refill
-    int slot_stride;                       // backward: floats per private gradient slot (0 = shared atomics)
-    long long B, L, W;                     // W >= 1
+    long long items[kMaxDepth + 1];       // thread items per degree
+    long long item_start[kMaxDepth + 2];  // first item of each degree in the packed order; [depth+1] = total
+    int tiles;                            // letter tiles per dense prefix
+    int chunk;                            // steps staged per refill
+    int slot_stride;                      // backward: scalars per private gradient slot (0 = shared atomics)
+    long long B, L, W;                    // W >= 1
     const int *windows;
 };
 
@@ -57,29 +57,52 @@ __device__ __forceinline__ void kahan_add(T &sum, T add, T &comp)
     }
 }
 
+// What one thread owns: degree K, the prefix u (|u| = K-1) and a tile of last letters.
+// Items of all degrees are packed into one index space (each degree padded to a warp
+// boundary), so a block may hold warps of several degrees; the per-step work is dispatched on K
+// inside the step loop.
 struct Item {
-    long long u;   // code of the owned prefix (length K-1)
-    int b0;        // first last-letter of the tile
-    int nb;        // letters in the tile (0 = inactive thread)
+    int K;          // degree (1..depth); meaningless when nb == 0
+    long long idx;  // index of the item within its degree
+    long long u;    // code of the owned prefix
+    int b0;         // first last-letter of the tile
+    int nb;         // letters in the tile (0 = inactive thread)
 };
 
 template <int TB>
-__device__ __forceinline__ Item decode_item(const GenericPlan &p, int K, long long idx)
+__device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi)
 {
-    Item it{0, 0, 0};
-    if (idx >= p.items[K]) return it;
+    Item it{1, 0, 0, 0, 0};
+    if (gi >= p.item_start[p.lt.depth + 1]) return it;
+    int K = 1;
+    while (K < p.lt.depth && gi >= p.item_start[K + 1]) ++K;
+    it.K = K;
+    it.idx = gi - p.item_start[K];
+    if (it.idx >= p.items[K]) return it;  // padding between degrees
     const int d = p.lt.d;
     if (p.lt.words[K] == nullptr) {
-        it.u = idx / p.tiles;
-        it.b0 = (int)(idx % p.tiles) * TB;
+        it.u = it.idx / p.tiles;
+        it.b0 = (int)(it.idx % p.tiles) * TB;
         it.nb = min(TB, d - it.b0);
     } else {
-        const long long code = p.lt.words[K][idx];
+        const long long code = p.lt.words[K][it.idx];
         it.u = code / d;
         it.b0 = (int)(code % d);
         it.nb = 1;
     }
     return it;
+}
+
+// Letters of the prefix, first letter in let[0]; entries at and beyond K-1 are zero.
+__device__ __forceinline__ void prefix_letters(const Item &it, int d, int (&let)[kMaxDepth])
+{
+    long long c = it.u;
+#pragma unroll
+    for (int j = kMaxDepth - 2; j >= 0; --j) {
+        let[j] = 0;
+        if (j < it.K - 1) { let[j] = (int)(c % d); c /= d; }
+    }
+    let[kMaxDepth - 1] = 0;
 }
 
 __device__ __forceinline__ void unit_window(const GenericPlan &p, long long unit, long long &b, int &start, int &steps)
@@ -103,250 +126,124 @@ __device__ __forceinline__ void stage_increments(const T *__restrict__ x, int d,
     for (int i = threadIdx.x; i < n * d; i += kBlock) s_dx[i] = lo[i + d] - lo[i];
 }
 
+// ---- one forward step of an item of degree K (pref[j] = S(u[:j]), top[i] = S(u.b_i)) ----
 template <typename T, int K, int TB>
-__device__ void level_forward(const GenericPlan &p, long long unit, long long idx, const T *__restrict__ path,
-                              T *__restrict__ out, T *s_dx)
+__device__ __forceinline__ void forward_step(const T *dx, const int (&let)[kMaxDepth], const Item &it,
+                                             T (&pref)[kMaxDepth], T (&cpref)[kMaxDepth], T (&top)[TB], T (&ctop)[TB])
 {
-    const int d = p.lt.d;
-    const Item it = decode_item<TB>(p, K, idx);
-    int let[K > 1 ? K - 1 : 1];
-    {
-        long long c = it.u;
+    T xs[K > 1 ? K - 1 : 1];
 #pragma unroll
-        for (int j = K - 2; j >= 0; --j) { let[j] = (int)(c % d); c /= d; }
-    }
-    long long b; int start, steps;
-    unit_window(p, unit, b, start, steps);
-    const T *x = path + (b * p.L + start) * d;
-
-    T pref[K], cpref[K];   // pref[j] = S(u[:j]), j = 1..K-1
-    T top[TB], ctop[TB];   // S(u.b) for the tile
+    for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
+    // degree K: Horner chain over the prefixes of u, then one FMA per tile letter
+    T bc = T(1);
 #pragma unroll
-    for (int j = 0; j < K; ++j) { pref[j] = T(0); cpref[j] = T(0); }
+    for (int j = 1; j <= K - 1; ++j) bc = fma(bc, xs[j - 1] * recip<T>(K - j + 1), pref[j]);
 #pragma unroll
-    for (int i = 0; i < TB; ++i) { top[i] = T(0); ctop[i] = T(0); }
-
-    for (int c0 = 0; c0 < steps; c0 += p.chunk) {
-        const int n = min(p.chunk, steps - c0);
-        __syncthreads();
-        stage_increments(x, d, c0, n, s_dx);
-        __syncthreads();
-        if (it.nb == 0) continue;
-        for (int t = 0; t < n; ++t) {
-            const T *dx = s_dx + t * d;
-            T xs[K > 1 ? K - 1 : 1];
+    for (int i = 0; i < TB; ++i)
+        if (i < it.nb) kahan_add(top[i], bc * dx[it.b0 + i], ctop[i]);
+    // private copies of the lower prefixes, highest first so each reads old values
 #pragma unroll
-            for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
-            // degree K: Horner chain over the prefixes of u, then one FMA per tile letter
-            T bc = T(1);
+    for (int m = K - 1; m >= 1; --m) {
+        T bm = T(1);
 #pragma unroll
-            for (int j = 1; j <= K - 1; ++j) bc = fma(bc, xs[j - 1] * recip<T>(K - j + 1), pref[j]);
-#pragma unroll
-            for (int i = 0; i < TB; ++i)
-                if (i < it.nb) kahan_add(top[i], bc * dx[it.b0 + i], ctop[i]);
-            // private copies of the lower prefixes, highest first so each reads old values
-#pragma unroll
-            for (int m = K - 1; m >= 1; --m) {
-                T bm = T(1);
-#pragma unroll
-                for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
-                kahan_add(pref[m], bm * xs[m - 1], cpref[m]);
-            }
-        }
-    }
-    if (it.nb == 0) return;
-    T *row = out + unit * p.lt.total + p.lt.offset[K];
-    if (p.lt.words[K] == nullptr) {
-#pragma unroll
-        for (int i = 0; i < TB; ++i)
-            if (i < it.nb) row[it.u * d + it.b0 + i] = top[i];
-    } else {
-        row[idx] = top[0];
+        for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+        kahan_add(pref[m], bm * xs[m - 1], cpref[m]);
     }
 }
 
+// ---- forward step of the prefixes only (uncompensated), used to rebuild them for backward ----
+template <typename T, int K>
+__device__ __forceinline__ void prefix_step(const T *dx, const int (&let)[kMaxDepth], T (&pref)[kMaxDepth])
+{
+    T xs[K > 1 ? K - 1 : 1];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
+#pragma unroll
+    for (int m = K - 1; m >= 1; --m) {
+        T bm = T(1);
+#pragma unroll
+        for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+        pref[m] = fma(bm, xs[m - 1], pref[m]);
+    }
+}
+
+// ---- one reverse step of an item of degree K ----
+// Rolls pref back to the previous point, pushes the adjoints apref through the transposed
+// chains and adds this thread's share of dL/d(dx_t) into sg (private slot, or the block's
+// shared row with atomics).
 template <typename T, int K, int TB>
-__device__ void level_backward(const GenericPlan &p, long long unit, long long idx, const T *__restrict__ path,
-                               const T *__restrict__ sig, const T *__restrict__ grad, T *__restrict__ inc_grad,
-                               T *s_dx, T *s_gd)
+__device__ __forceinline__ void backward_step(const T *dx, const int (&let)[kMaxDepth], const Item &it,
+                                              T (&pref)[kMaxDepth], T (&apref)[kMaxDepth], const T (&g)[TB], T *sg,
+                                              bool slots)
 {
-    const int d = p.lt.d;
-    const Item it = decode_item<TB>(p, K, idx);
-    int let[K > 1 ? K - 1 : 1];
+    T xs[K > 1 ? K - 1 : 1], lg[K > 1 ? K - 1 : 1];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) { xs[j] = dx[let[j]]; lg[j] = T(0); }
+
+    // degrees 1..K-1 of the private chain: undo the step, then transpose it
+#pragma unroll
+    for (int m = 1; m <= K - 1; ++m) {
+        T bc[K];  // bc[j] = Horner value after prefix length j (bc[0] = 1)
+        bc[0] = T(1);
+#pragma unroll
+        for (int j = 1; j <= m - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(m - j + 1), pref[j]);
+        pref[m] = fma(-bc[m - 1], xs[m - 1], pref[m]);
+        const T a = apref[m];
+        lg[m - 1] = fma(a, bc[m - 1], lg[m - 1]);
+        T adj = a * xs[m - 1];
+#pragma unroll
+        for (int j = m - 1; j >= 1; --j) {
+            apref[j] += adj;
+            const T c = recip<T>(m - j + 1);
+            lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
+            adj = adj * (xs[j - 1] * c);
+        }
+    }
+    // degree K: the tile
     {
-        long long c = it.u;
+        T bc[K];
+        bc[0] = T(1);
 #pragma unroll
-        for (int j = K - 2; j >= 0; --j) { let[j] = (int)(c % d); c /= d; }
-    }
-    long long b; int start, steps;
-    unit_window(p, unit, b, start, steps);
-    if (steps == 0) return;  // uniform over the block
-    const T *x = path + (b * p.L + start) * d;
-    T *gd = inc_grad + (b * (p.L - 1) + start) * d;
-
-    T pref[K], apref[K];
-    T g[TB];
+        for (int j = 1; j <= K - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(K - j + 1), pref[j]);
+        T adj = T(0);
 #pragma unroll
-    for (int j = 0; j < K; ++j) { pref[j] = T(0); apref[j] = T(0); }
-#pragma unroll
-    for (int i = 0; i < TB; ++i) g[i] = T(0);
-
-    if (it.nb > 0) {
-        const T *grow = grad + unit * p.lt.total + p.lt.offset[K];
-        if (p.lt.words[K] == nullptr) {
-#pragma unroll
-            for (int i = 0; i < TB; ++i)
-                if (i < it.nb) g[i] = grow[it.u * d + it.b0 + i];
-        } else {
-            g[0] = grow[idx];
-        }
-    }
-
-    // Prefix values at the end of the unit: read them from the saved signature while all
-    // lower degrees are stored dense, otherwise recompute them with a forward sweep.
-    if (p.lt.lower_dense[K]) {
-        if (it.nb > 0) {
-            const T *srow = sig + unit * p.lt.total;
-            long long c = it.u;
-#pragma unroll
-            for (int j = K - 1; j >= 1; --j) { pref[j] = srow[p.lt.dense_offset[j] + c]; c /= d; }
-        }
-    } else {
-        for (int c0 = 0; c0 < steps; c0 += p.chunk) {
-            const int n = min(p.chunk, steps - c0);
-            __syncthreads();
-            stage_increments(x, d, c0, n, s_dx);
-            __syncthreads();
-            if (it.nb == 0) continue;
-            for (int t = 0; t < n; ++t) {
-                const T *dx = s_dx + t * d;
-                T xs[K > 1 ? K - 1 : 1];
-#pragma unroll
-                for (int j = 0; j < K - 1; ++j) xs[j] = dx[let[j]];
-#pragma unroll
-                for (int m = K - 1; m >= 1; --m) {
-                    T bm = T(1);
-#pragma unroll
-                    for (int j = 1; j <= m - 1; ++j) bm = fma(bm, xs[j - 1] * recip<T>(m - j + 1), pref[j]);
-                    pref[m] = fma(bm, xs[m - 1], pref[m]);
-                }
+        for (int i = 0; i < TB; ++i) {
+            if (i < it.nb) {
+                adj = fma(g[i], dx[it.b0 + i], adj);
+                if (slots) sg[it.b0 + i] += g[i] * bc[K - 1];
+                else atomicAdd(&sg[it.b0 + i], g[i] * bc[K - 1]);
             }
         }
+#pragma unroll
+        for (int j = K - 1; j >= 1; --j) {
+            apref[j] += adj;
+            const T c = recip<T>(K - j + 1);
+            lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
+            adj = adj * (xs[j - 1] * c);
+        }
     }
-
-    // Reverse sweep, chunk by chunk from the end.
-    const bool slots = p.slot_stride > 0;
-    const long long block_first = idx - threadIdx.x;  // item index of thread 0 of this block
-    const int nact = (int)max(0LL, min((long long)kBlock, p.items[K] - block_first));
-    const int nchunks = (steps + p.chunk - 1) / p.chunk;
-    for (int ci = nchunks - 1; ci >= 0; --ci) {
-        const int c0 = ci * p.chunk;
-        const int n = min(p.chunk, steps - c0);
-        __syncthreads();
-        stage_increments(x, d, c0, n, s_dx);
-        if (!slots)
-            for (int i = threadIdx.x; i < n * d; i += kBlock) s_gd[i] = T(0);
-        __syncthreads();
-        if (it.nb > 0) {
-            for (int t = n - 1; t >= 0; --t) {
-                const T *dx = s_dx + t * d;
-                // where this step's increment gradients go: the block's shared row (atomics), or
-                // this thread's private slot, zeroed first
-                T *sg = slots ? s_gd + ((size_t)t * kBlock + threadIdx.x) * p.slot_stride : s_gd + t * d;
-                if (slots)
-                    for (int a = 0; a < d; ++a) sg[a] = T(0);
-                T xs[K > 1 ? K - 1 : 1], lg[K > 1 ? K - 1 : 1];
 #pragma unroll
-                for (int j = 0; j < K - 1; ++j) { xs[j] = dx[let[j]]; lg[j] = T(0); }
-
-                // degrees 1..K-1 of the private chain: undo the step, then transpose it
-#pragma unroll
-                for (int m = 1; m <= K - 1; ++m) {
-                    T bc[K];  // bc[j] = Horner value after prefix length j (bc[0] = 1)
-                    bc[0] = T(1);
-#pragma unroll
-                    for (int j = 1; j <= m - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(m - j + 1), pref[j]);
-                    pref[m] = fma(-bc[m - 1], xs[m - 1], pref[m]);
-                    const T a = apref[m];
-                    lg[m - 1] = fma(a, bc[m - 1], lg[m - 1]);
-                    T adj = a * xs[m - 1];
-#pragma unroll
-                    for (int j = m - 1; j >= 1; --j) {
-                        apref[j] += adj;
-                        const T c = recip<T>(m - j + 1);
-                        lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
-                        adj = adj * (xs[j - 1] * c);
-                    }
-                }
-                // degree K: the tile
-                {
-                    T bc[K];
-                    bc[0] = T(1);
-#pragma unroll
-                    for (int j = 1; j <= K - 1; ++j) bc[j] = fma(bc[j - 1], xs[j - 1] * recip<T>(K - j + 1), pref[j]);
-                    T adj = T(0);
-#pragma unroll
-                    for (int i = 0; i < TB; ++i) {
-                        if (i < it.nb) {
-                            adj = fma(g[i], dx[it.b0 + i], adj);
-                            if (slots) sg[it.b0 + i] += g[i] * bc[K - 1];
-                            else atomicAdd(&sg[it.b0 + i], g[i] * bc[K - 1]);
-                        }
-                    }
-#pragma unroll
-                    for (int j = K - 1; j >= 1; --j) {
-                        apref[j] += adj;
-                        const T c = recip<T>(K - j + 1);
-                        lg[j - 1] = fma(adj * c, bc[j - 1], lg[j - 1]);
-                        adj = adj * (xs[j - 1] * c);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < K - 1; ++j) {
-                    if (slots) sg[let[j]] += lg[j];
-                    else atomicAdd(&sg[let[j]], lg[j]);
-                }
-            }
-        }
-        __syncthreads();
-        for (int i = threadIdx.x; i < n * d; i += kBlock) {
-            T v;
-            if (slots) {
-                // fixed-order sum over the active threads' slots
-                const int t = i / d, a = i - t * d;
-                const T *col = s_gd + (size_t)t * kBlock * p.slot_stride + a;
-                v = T(0);
-                for (int thr = 0; thr < nact; ++thr) v += col[(size_t)thr * p.slot_stride];
-            } else {
-                v = s_gd[i];
-            }
-            if (v != T(0)) atomicAdd(&gd[(long long)c0 * d + i], v);
-        }
+    for (int j = 0; j < K - 1; ++j) {
+        if (slots) sg[let[j]] += lg[j];
+        else atomicAdd(&sg[let[j]], lg[j]);
     }
 }
 
-#define PSIG_SWITCH_DEGREE(k, CALL)                                   \
-    switch (k) {                                                      \
-        case 1: { constexpr int K = 1; CALL; } break;                 \
-        case 2: { constexpr int K = 2; CALL; } break;                 \
-        case 3: { constexpr int K = 3; CALL; } break;                 \
-        case 4: { constexpr int K = 4; CALL; } break;                 \
-        case 5: { constexpr int K = 5; CALL; } break;                 \
-        case 6: { constexpr int K = 6; CALL; } break;                 \
-        case 7: { constexpr int K = 7; CALL; } break;                 \
-        case 8: { constexpr int K = 8; CALL; } break;                 \
-        case 9: { constexpr int K = 9; CALL; } break;                 \
-        case 10: { constexpr int K = 10; CALL; } break;               \
-        case 11: { constexpr int K = 11; CALL; } break;               \
-        default: { constexpr int K = 12; CALL; } break;               \
+#define PSIG_SWITCH_DEGREE(k, ...)                                           \
+    switch (k) {                                                             \
+        case 1: { constexpr int K = 1; __VA_ARGS__; } break;                 \
+        case 2: { constexpr int K = 2; __VA_ARGS__; } break;                 \
+        case 3: { constexpr int K = 3; __VA_ARGS__; } break;                 \
+        case 4: { constexpr int K = 4; __VA_ARGS__; } break;                 \
+        case 5: { constexpr int K = 5; __VA_ARGS__; } break;                 \
+        case 6: { constexpr int K = 6; __VA_ARGS__; } break;                 \
+        case 7: { constexpr int K = 7; __VA_ARGS__; } break;                 \
+        case 8: { constexpr int K = 8; __VA_ARGS__; } break;                 \
+        case 9: { constexpr int K = 9; __VA_ARGS__; } break;                 \
+        case 10: { constexpr int K = 10; __VA_ARGS__; } break;               \
+        case 11: { constexpr int K = 11; __VA_ARGS__; } break;               \
+        default: { constexpr int K = 12; __VA_ARGS__; } break;               \
     }
-
-__device__ __forceinline__ int block_degree(const GenericPlan &p)
-{
-    int k = 1;
-    while (k < p.lt.depth && (long long)blockIdx.x >= p.first_block[k + 1]) ++k;
-    return k;
-}
 
 template <typename T, int TB>
 __global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan p, const T *__restrict__ path,
@@ -354,11 +251,43 @@ __global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan 
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T *s_dx = reinterpret_cast<T *>(smem_raw);
-    const int k = block_degree(p);
-    const long long idx = ((long long)blockIdx.x - p.first_block[k]) * kBlock + threadIdx.x;
+    const int d = p.lt.d;
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kBlock + threadIdx.x);
+    int let[kMaxDepth];
+    prefix_letters(it, d, let);
     const long long units = p.B * p.W;
+
     for (long long unit = blockIdx.y; unit < units; unit += gridDim.y) {
-        PSIG_SWITCH_DEGREE(k, (level_forward<T, K, TB>(p, unit, idx, path, out, s_dx)));
+        long long b; int start, steps;
+        unit_window(p, unit, b, start, steps);
+        const T *x = path + (b * p.L + start) * d;
+
+        T pref[kMaxDepth], cpref[kMaxDepth], top[TB], ctop[TB];
+#pragma unroll
+        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); cpref[j] = T(0); }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) { top[i] = T(0); ctop[i] = T(0); }
+
+        for (int c0 = 0; c0 < steps; c0 += p.chunk) {
+            const int n = min(p.chunk, steps - c0);
+            __syncthreads();
+            stage_increments(x, d, c0, n, s_dx);
+            __syncthreads();
+            if (it.nb == 0) continue;
+            // dispatch on the degree once per chunk, so the step loop itself is branch-free
+            PSIG_SWITCH_DEGREE(it.K, {
+                for (int t = 0; t < n; ++t) forward_step<T, K, TB>(s_dx + t * d, let, it, pref, cpref, top, ctop);
+            });
+        }
+        if (it.nb == 0) continue;
+        T *row = out + unit * p.lt.total + p.lt.offset[it.K];
+        if (p.lt.words[it.K] == nullptr) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i)
+                if (i < it.nb) row[it.u * d + it.b0 + i] = top[i];
+        } else {
+            row[it.idx] = top[0];
+        }
     }
 }
 
@@ -371,11 +300,106 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T *s_dx = reinterpret_cast<T *>(smem_raw);
     T *s_gd = s_dx + (size_t)p.chunk * p.lt.d;
-    const int k = block_degree(p);
-    const long long idx = ((long long)blockIdx.x - p.first_block[k]) * kBlock + threadIdx.x;
+    const int d = p.lt.d;
+    const long long block_first = (long long)blockIdx.x * kBlock;
+    const Item it = decode_item<TB>(p, block_first + threadIdx.x);
+    int let[kMaxDepth];
+    prefix_letters(it, d, let);
+    const bool slots = p.slot_stride > 0;
+    const int nact = (int)max(0LL, min((long long)kBlock, p.item_start[p.lt.depth + 1] - block_first));
+    // does any item of this block have to rebuild its prefix values with a forward sweep?
+    const bool rebuild = it.nb > 0 && !p.lt.lower_dense[it.K];
+    const bool any_rebuild = __syncthreads_or(rebuild ? 1 : 0) != 0;
     const long long units = p.B * p.W;
+
     for (long long unit = blockIdx.y; unit < units; unit += gridDim.y) {
-        PSIG_SWITCH_DEGREE(k, (level_backward<T, K, TB>(p, unit, idx, path, sig, grad, inc_grad, s_dx, s_gd)));
+        long long b; int start, steps;
+        unit_window(p, unit, b, start, steps);
+        if (steps == 0) continue;  // uniform over the block
+        const T *x = path + (b * p.L + start) * d;
+        T *gd = inc_grad + (b * (p.L - 1) + start) * d;
+
+        T pref[kMaxDepth], apref[kMaxDepth], g[TB];
+#pragma unroll
+        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); apref[j] = T(0); }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) g[i] = T(0);
+
+        if (it.nb > 0) {
+            const T *grow = grad + unit * p.lt.total + p.lt.offset[it.K];
+            if (p.lt.words[it.K] == nullptr) {
+#pragma unroll
+                for (int i = 0; i < TB; ++i)
+                    if (i < it.nb) g[i] = grow[it.u * d + it.b0 + i];
+            } else {
+                g[0] = grow[it.idx];
+            }
+            // Prefix values at the end of the unit: read from the saved signature while all
+            // lower degrees are stored dense ...
+            if (!rebuild) {
+                const T *srow = sig + unit * p.lt.total;
+                long long c = it.u;
+#pragma unroll
+                for (int j = kMaxDepth - 1; j >= 1; --j)
+                    if (j <= it.K - 1) { pref[j] = srow[p.lt.dense_offset[j] + c]; c /= d; }
+            }
+        }
+        // ... otherwise recompute them with a forward sweep.
+        if (any_rebuild) {
+            for (int c0 = 0; c0 < steps; c0 += p.chunk) {
+                const int n = min(p.chunk, steps - c0);
+                __syncthreads();
+                stage_increments(x, d, c0, n, s_dx);
+                __syncthreads();
+                if (!rebuild) continue;
+                PSIG_SWITCH_DEGREE(it.K, {
+                    for (int t = 0; t < n; ++t) prefix_step<T, K>(s_dx + t * d, let, pref);
+                });
+            }
+        }
+
+        // Reverse sweep, chunk by chunk from the end.
+        const int nchunks = (steps + p.chunk - 1) / p.chunk;
+        for (int ci = nchunks - 1; ci >= 0; --ci) {
+            const int c0 = ci * p.chunk;
+            const int n = min(p.chunk, steps - c0);
+            __syncthreads();
+            stage_increments(x, d, c0, n, s_dx);
+            if (!slots)
+                for (int i = threadIdx.x; i < n * d; i += kBlock) s_gd[i] = T(0);
+            __syncthreads();
+            // Where a step's increment gradients go: the block's shared row (atomics), or this
+            // thread's private slot, zeroed first.  Padding threads between two degrees only zero
+            // theirs (the column sums below run over them too).
+            if (slots && (int)threadIdx.x < nact) {
+                for (int t = 0; t < n; ++t) {
+                    T *sg = s_gd + ((size_t)t * kBlock + threadIdx.x) * p.slot_stride;
+                    for (int a = 0; a < d; ++a) sg[a] = T(0);
+                }
+            }
+            if (it.nb > 0) {
+                const size_t t_stride = slots ? (size_t)kBlock * p.slot_stride : (size_t)d;
+                T *sg0 = slots ? s_gd + (size_t)threadIdx.x * p.slot_stride : s_gd;
+                PSIG_SWITCH_DEGREE(it.K, {
+                    for (int t = n - 1; t >= 0; --t)
+                        backward_step<T, K, TB>(s_dx + t * d, let, it, pref, apref, g, sg0 + t * t_stride, slots);
+                });
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < n * d; i += kBlock) {
+                T v;
+                if (slots) {
+                    // fixed-order sum over the active threads' slots
+                    const int t = i / d, a = i - t * d;
+                    const T *col = s_gd + (size_t)t * kBlock * p.slot_stride + a;
+                    v = T(0);
+                    for (int thr = 0; thr < nact; ++thr) v += col[(size_t)thr * p.slot_stride];
+                } else {
+                    v = s_gd[i];
+                }
+                if (v != T(0)) atomicAdd(&gd[(long long)c0 * d + i], v);
+            }
+        }
     }
 }
 
@@ -411,16 +435,19 @@ int make_plan(const PsigSigDesc &desc, const LevelTable &lt, int buffers, Generi
     p.W = desc.W > 0 ? desc.W : 1;
     p.windows = desc.W > 0 ? desc.windows : nullptr;
     p.tiles = (lt.d + TB - 1) / TB;
-    long long blocks = 0;
+    long long total_items = 0;
     long long d_pow = 1;  // d^(k-1)
     for (int k = 1; k <= lt.depth; ++k) {
         p.items[k] = lt.words[k] ? lt.size[k] : (lt.size[k] == 0 ? 0 : d_pow * p.tiles);
-        p.first_block[k] = blocks;
-        blocks += (p.items[k] + kBlock - 1) / kBlock;
+        // every degree starts on a warp boundary: a warp never mixes degrees (no divergence in
+        // the per-step dispatch), a block may hold warps of different degrees
+        total_items = (total_items + 31) / 32 * 32;
+        p.item_start[k] = total_items;
+        total_items += p.items[k];
         if (k < lt.depth) d_pow *= lt.d;
     }
-    for (int k = lt.depth + 1; k <= kMaxDepth + 1; ++k) p.first_block[k] = blocks;
-    if (blocks > 0x7fffffffLL) return PSIG_ERR_TOO_LARGE;
+    for (int k = lt.depth + 1; k <= kMaxDepth + 1; ++k) p.item_start[k] = total_items;
+    if ((total_items + kBlock - 1) / kBlock > 0x7fffffffLL) return PSIG_ERR_TOO_LARGE;
     const size_t per_step = sizeof(T) * (size_t)lt.d * buffers;
     if (per_step > 48 * 1024) return PSIG_ERR_TOO_LARGE;
     long long chunk = (long long)(kStageBytes / per_step);
@@ -453,7 +480,7 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
     const int rc = make_plan<T>(desc, lt, 1, &plan);
     if (rc != PSIG_OK) return rc;
     const long long units = plan.B * plan.W;
-    const long long blocks = plan.first_block[kMaxDepth + 1];
+    const long long blocks = (plan.item_start[kMaxDepth + 1] + kBlock - 1) / kBlock;
     if (units == 0 || blocks == 0) return PSIG_OK;
     const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
     const size_t smem = sizeof(T) * (size_t)plan.chunk * lt.d;
@@ -470,7 +497,7 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
     const int rc = make_plan<T>(desc, lt, 2, &plan);
     if (rc != PSIG_OK) return rc;
     const long long units = plan.B * plan.W;
-    const long long blocks = plan.first_block[kMaxDepth + 1];
+    const long long blocks = (plan.item_start[kMaxDepth + 1] + kBlock - 1) / kBlock;
     if (desc.B == 0) return PSIG_OK;
     const size_t inc_bytes = sizeof(T) * (size_t)desc.B * (size_t)(desc.L - 1) * lt.d;
     if (cudaMemsetAsync(inc_grad_ws, 0, inc_bytes, stream) != cudaSuccess) return PSIG_ERR_CUDA;
