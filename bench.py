@@ -384,6 +384,36 @@ def cpu_baseline(name, threads=None, seconds_hint=15.0):
                       f"(work is linear in B); port of the reference per-word algorithm, OpenMP over paths"}, dt
 
 
+def reference_cuda_baseline(wl, device, steps=5, warmup=2):
+    """The reference's own CUDA operators (built unchanged into oracle/_ref/ by oracle/build_ref.py)
+    on the same tensors, as a reported baseline.  Returns None when that library is not there."""
+    lib = os.path.join(ROOT, "oracle", "_ref", "libpathsig_ops.so")
+    if not os.path.isfile(lib) or wl.spec["kind"] == "loglyndon":
+        return None
+    try:
+        torch.ops.load_library(lib)
+        ref = torch.ops.pathsig
+        m = wl.mod
+        args = (m.depth, m.alternative_projection, m._encoded_words, list(m._level_sizes), m.use_windows, m._windows)
+
+        def fwd():
+            return ref.compute_signature(wl.x, *args)
+
+        def fwd_bwd():
+            sig = ref.compute_signature(wl.x, *args)
+            return ref.signature_backward(wl.x, sig, wl.G, *args)
+
+        ms_f = time_steps(fwd, steps, warmup, 1, device)
+        ms_fb = time_steps(fwd_bwd, steps, warmup, 1, device)
+        return {"fwd": {"value": wl.units * steps / (ms_f * 1e-3), "ms_per_step": ms_f / steps},
+                "fwd_bwd": {"value": wl.units * steps / (ms_fb * 1e-3), "ms_per_step": ms_fb / steps},
+                "unit": UNIT, "steps": steps,
+                "what": "reference CUDA operators compiled for sm_100 from its unchanged sources, same tensors, "
+                        "device-timed; a reported baseline, not part of the product"}
+    except Exception as exc:  # the baseline must never break the benchmark
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
+
 # ----------------------------------------------------------------------------------------------
 # arms
 # ----------------------------------------------------------------------------------------------
@@ -585,8 +615,10 @@ def run_ours(args):
             torch.cuda.empty_cache()
 
     cpu = None
+    ref_cuda = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, _ = cpu_baseline(name)
+        ref_cuda = reference_cuda_baseline(wl, device)
 
     if rank != 0:
         return
@@ -619,6 +651,7 @@ def run_ours(args):
                          "unit": "GB/s", "frac": main["hbm_gbs_fwd_bwd"] / (hbm_peak * world) if hbm_peak else None,
                          "peak_source": hbm_src, "bytes": "read path + write signature + read grad + write grad_path"},
         "cpu_baseline": cpu,
+        "reference_cuda": ref_cuda,
         "others": others,
     }
     print(json.dumps(line), flush=True)
