@@ -2,6 +2,8 @@
 // the device it runs on (the roofline denominator of the signature kernels).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace psig {
 namespace {
 
@@ -23,12 +25,36 @@ __global__ void __launch_bounds__(256) ffma_probe(float *out, int iters, float a
     if (s == 12345.678f) out[0] = s;  // keeps the loop alive without a store in practice
 }
 
+// Same loop with the packed two-lane FP32 FMA of sm_100 (fma.rn.f32x2): 2 FMAs per instruction.
+__global__ void __launch_bounds__(256) ffma2_probe(float *out, int iters, float a, float b)
+{
+    float2 r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = make_float2((float)(threadIdx.x + i) * 1e-3f, (float)(threadIdx.x - i) * 1e-3f);
+    const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int rep = 0; rep < 8; ++rep) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = __ffma2_rn(r[i], a2, b2);
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += r[i].x + r[i].y;
+    if (s == 12345.678f) out[0] = s;
+}
+
 }  // namespace
 }  // namespace psig
 
 extern "C" int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream)
 {
     if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
+    if (iters < 0x40000000 && getenv("PSIG_PROBE_PACKED"))  // experiment switch: packed f32x2 variant
+        psig::ffma2_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
+                                                                               0.999999f, 1e-7f);
+    else
     psig::ffma_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
                                                                           0.999999f, 1e-7f);
     if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;

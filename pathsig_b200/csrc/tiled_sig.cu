@@ -39,6 +39,7 @@ struct Shape {
     static_assert(D % DA == 0, "DA must divide D");
     static constexpr int Q = N - P;  // depth of the register sub-tree
     static_assert(Q <= 3, "sub-tree depth above 3 is not implemented");
+    static_assert(D % 2 == 0 && DA % 2 == 0, "packed FMAs pair neighbouring letters");
     static constexpr int SPLIT = D / DA;
     static constexpr int TPU = ipow(D, P) * SPLIT;  // threads per (path, window) unit
     static constexpr int n1 = DA;
@@ -195,6 +196,23 @@ __device__ __forceinline__ void scaled_increments_from_points(const float *raw, 
     }
 }
 
+#ifndef PSIG_PACKED_FMA
+#define PSIG_PACKED_FMA 1
+#endif
+// (x0, x1) += (a0, a1) * (b0, b1): one packed two-lane FMA (fma.rn.f32x2 of sm_100) instead of two
+// scalar ones.  Same arithmetic and rounding per lane; it halves the issue slots of the inner loops.
+__device__ __forceinline__ void fma_pair(float &x0, float &x1, float a0, float a1, float b0, float b1)
+{
+#if PSIG_PACKED_FMA
+    const float2 r = __ffma2_rn(make_float2(a0, a1), make_float2(b0, b1), make_float2(x0, x1));
+    x0 = r.x;
+    x1 = r.y;
+#else
+    x0 = fmaf(a0, b0, x0);
+    x1 = fmaf(a1, b1, x1);
+#endif
+}
+
 // The operands one step needs: the increment at this thread's prefix letters, the full
 // increment vector, and the (scaled) slices at the owned first letters.
 template <int D, int DA, int P, int Q>
@@ -259,7 +277,8 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
             for (int c = 0; c < D; ++c) {
                 const float v2 = fmaf(v1, o.dxf2[c], s.R2[a * D + c]);
 #pragma unroll
-                for (int e = 0; e < D; ++e) s.R3[(a * D + c) * D + e] = fmaf(v2, o.dxf1[e], s.R3[(a * D + c) * D + e]);
+                for (int e = 0; e < D; e += 2)
+                    fma_pair(s.R3[(a * D + c) * D + e], s.R3[(a * D + c) * D + e + 1], v2, v2, o.dxf1[e], o.dxf1[e + 1]);
             }
         }
     }
@@ -272,7 +291,8 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
         for (int a = 0; a < DA; ++a) {
             const float v1 = fmaf(bb, o.dxa2[a], s.R1[a]);
 #pragma unroll
-            for (int c = 0; c < D; ++c) s.R2[a * D + c] = fmaf(v1, o.dxf1[c], s.R2[a * D + c]);
+            for (int c = 0; c < D; c += 2)
+                fma_pair(s.R2[a * D + c], s.R2[a * D + c + 1], v1, v1, o.dxf1[c], o.dxf1[c + 1]);
         }
     }
     {  // target degree P+1
@@ -281,7 +301,7 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
 #pragma unroll
         for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
 #pragma unroll
-        for (int a = 0; a < DA; ++a) s.R1[a] = fmaf(bb, o.dxa1[a], s.R1[a]);
+        for (int a = 0; a < DA; a += 2) fma_pair(s.R1[a], s.R1[a + 1], bb, bb, o.dxa1[a], o.dxa1[a + 1]);
     }
     // the shared prefixes, highest first so each reads the previous step's lower values
 #pragma unroll
@@ -505,14 +525,14 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
         float bc[P + 1];
         head_chain<P, k>(bc, o.xs, s.pref);
         const float bb = bc[P];
-        float adj = 0.f;
+        float adj0 = 0.f, adj1 = 0.f;
 #pragma unroll
-        for (int a = 0; a < DA; ++a) {
-            if constexpr (Q >= 2) s.RS1[a] = fmaf(-bb, o.dxa1[a], s.RS1[a]);
-            adj = fmaf(s.RG1[a], o.dxa1[a], adj);
-            gda[a] = fmaf(s.RG1[a], bb, gda[a]);
+        for (int a = 0; a < DA; a += 2) {
+            if constexpr (Q >= 2) fma_pair(s.RS1[a], s.RS1[a + 1], -bb, -bb, o.dxa1[a], o.dxa1[a + 1]);
+            fma_pair(adj0, adj1, s.RG1[a], s.RG1[a + 1], o.dxa1[a], o.dxa1[a + 1]);
+            fma_pair(gda[a], gda[a + 1], s.RG1[a], s.RG1[a + 1], bb, bb);
         }
-        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+        back_chain<P, k>(adj0 + adj1, bc, o.xs, s.apref, lg);
     }
     if constexpr (Q >= 2) {  // target degree P+2
         constexpr int k = P + 2;
@@ -523,14 +543,16 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
 #pragma unroll
         for (int a = 0; a < DA; ++a) {
             const float v1 = fmaf(bb, o.dxa2[a], s.RS1[a]);
-            float av = 0.f;
+            float av_even = 0.f, av_odd = 0.f;
 #pragma unroll
-            for (int c = 0; c < D; ++c) {
-                if constexpr (Q >= 3) s.RS2[a * D + c] = fmaf(-v1, o.dxf1[c], s.RS2[a * D + c]);
-                const float g = s.RG2[a * D + c];
-                av = fmaf(g, o.dxf1[c], av);
-                gdf[c] = fmaf(g, v1, gdf[c]);
+            for (int c = 0; c < D; c += 2) {
+                if constexpr (Q >= 3)
+                    fma_pair(s.RS2[a * D + c], s.RS2[a * D + c + 1], -v1, -v1, o.dxf1[c], o.dxf1[c + 1]);
+                const float g0 = s.RG2[a * D + c], g1 = s.RG2[a * D + c + 1];
+                fma_pair(av_even, av_odd, g0, g1, o.dxf1[c], o.dxf1[c + 1]);
+                fma_pair(gdf[c], gdf[c + 1], g0, g1, v1, v1);
             }
+            const float av = av_even + av_odd;
             s.RG1[a] += av;
             adj = fmaf(av, o.dxa2[a], adj);
             gda[a] = fmaf(av * 0.5f, bb, gda[a]);
@@ -550,13 +572,14 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
 #pragma unroll
             for (int c = 0; c < D; ++c) {
                 const float v2 = fmaf(v1, o.dxf2[c], s.RS2[a * D + c]);
-                float av2 = 0.f;
+                float av2_even = 0.f, av2_odd = 0.f;
 #pragma unroll
-                for (int e = 0; e < D; ++e) {
-                    const float g = s.RG3[(a * D + c) * D + e];
-                    av2 = fmaf(g, o.dxf1[e], av2);
-                    gdf[e] = fmaf(g, v2, gdf[e]);
+                for (int e = 0; e < D; e += 2) {
+                    const float g0 = s.RG3[(a * D + c) * D + e], g1 = s.RG3[(a * D + c) * D + e + 1];
+                    fma_pair(av2_even, av2_odd, g0, g1, o.dxf1[e], o.dxf1[e + 1]);
+                    fma_pair(gdf[e], gdf[e + 1], g0, g1, v2, v2);
                 }
+                const float av2 = av2_even + av2_odd;
                 s.RG2[a * D + c] += av2;
                 av1 = fmaf(av2, o.dxf2[c], av1);
                 gdf[c] = fmaf(av2 * 0.5f, v1, gdf[c]);
