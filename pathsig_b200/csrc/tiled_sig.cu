@@ -52,7 +52,9 @@ struct Shape {
         return o;
     }
     static constexpr long long TOTAL = dense_off(N + 1);
-    static constexpr bool kVecLayout = (D % 4 == 0) && (DA % 4 == 0);
+    // 128-bit global accesses: runs at degree P+1 start at u*D + a0, deeper runs at multiples of D
+    static constexpr bool kVecFirst = (D % 4 == 0) && (DA % 4 == 0);
+    static constexpr bool kVecDeep = (D % 4 == 0);
 };
 
 template <int LEN>
@@ -423,7 +425,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     // the top_size requested words of degree N in the caller's order.
     const long long width = PROJ ? S::dense_off(N) + top_size : S::TOTAL;
     float *row = out + unit * width;
-    const bool vec = S::kVecLayout && vec_ok;
+    const bool vec1 = S::kVecFirst && vec_ok, vec = S::kVecDeep && vec_ok;
 #pragma unroll
     for (int j = 1; j <= P; ++j) {
         const int span = ipow(D, P - j) * S::SPLIT;  // threads sharing the prefix of length j
@@ -431,7 +433,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     }
     const long long base1 = (long long)u * D + a0;
     if constexpr (!PROJ) {
-        store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+        store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
         if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
         if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
     } else {
@@ -440,10 +442,10 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
         if constexpr (Q == 1) {
             store_run<S::n1>(s_top + base1, st.R1, true);
         } else if constexpr (Q == 2) {
-            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
             store_run<S::n2>(s_top + base1 * D, st.R2, true);
         } else {
-            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec);
+            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
             store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
             store_run<S::n3>(s_top + base1 * D * D, st.R3, true);
         }
@@ -675,7 +677,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     const float *x = path + (b * L + start) * D;
     float *gx = grad_path + (b * L + start) * D;  // gradient at the first point of the unit
 
-    const bool vec = S::kVecLayout && vec_ok;
+    const bool vec1 = S::kVecFirst && vec_ok, vec = S::kVecDeep && vec_ok;
     const long long width = top_words ? S::dense_off(N) + top_size : S::TOTAL;
     const float *srow = sig + unit * width;
     const float *grow = grad + unit * width;
@@ -691,10 +693,10 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         // the incoming gradient of a shared prefix is seeded in exactly one of its threads
         st.apref[j] = (split == 0 && u % span == 0) ? grow[idx] : 0.f;
     }
-    if constexpr (Q >= 2) load_run<S::n1>(st.RS1, srow + S::dense_off(P + 1) + base1, vec);
+    if constexpr (Q >= 2) load_run<S::n1>(st.RS1, srow + S::dense_off(P + 1) + base1, vec1);
     if constexpr (Q >= 3) load_run<S::n2>(st.RS2, srow + S::dense_off(P + 2) + base1 * D, vec);
     if (top_words == nullptr) {
-        load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+        load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec1);
         if constexpr (Q >= 2) load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
         if constexpr (Q >= 3) load_run<S::n3>(st.RG3, grow + S::dense_off(P + 3) + base1 * D * D, vec);
     } else {
@@ -708,10 +710,10 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         if constexpr (Q == 1) {
             load_run<S::n1>(st.RG1, s_top + base1, true);
         } else if constexpr (Q == 2) {
-            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec1);
             load_run<S::n2>(st.RG2, s_top + base1 * D, true);
         } else {
-            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec);
+            load_run<S::n1>(st.RG1, grow + S::dense_off(P + 1) + base1, vec1);
             load_run<S::n2>(st.RG2, grow + S::dense_off(P + 2) + base1 * D, vec);
             load_run<S::n3>(st.RG3, s_top + base1 * D * D, true);
         }
@@ -796,9 +798,10 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
 // ------------------------------------------------------------------------------------------
 // configurations
 // ------------------------------------------------------------------------------------------
-template <int D_, int N_, int P_, int DAF_, int NTF_, int MINBF_, int DAB_, int NTB_, int CHR_, int MINBB_>
+template <int D_, int N_, int PF_, int DAF_, int NTF_, int MINBF_, int PB_, int DAB_, int NTB_, int CHR_, int MINBB_>
 struct Config {
-    static constexpr int D = D_, N = N_, P = P_;
+    static constexpr int D = D_, N = N_;
+    static constexpr int PF = PF_, PB = PB_;  // prefix length owned by a thread, forward / backward
     static constexpr int DAF = DAF_, NTF = NTF_, MINBF = MINBF_;            // forward: first-letter tile, block, min blocks/SM
     static constexpr int DAB = DAB_, NTB = NTB_, CHR = CHR_, MINBB = MINBB_;  // backward
 };
@@ -847,10 +850,16 @@ struct Config {
 #ifndef PSIG_164_MINBB
 #define PSIG_164_MINBB 1
 #endif
-#define PSIG_CFG_8_4 8, 4, 2, PSIG_84_DAF, PSIG_84_NTF, PSIG_84_MINBF, PSIG_84_DAB, PSIG_84_NTB, PSIG_84_CHR, PSIG_84_MINBB
-#define PSIG_CFG_16_4 16, 4, 2, PSIG_164_DAF, PSIG_164_NTF, PSIG_164_MINBF, PSIG_164_DAB, PSIG_164_NTB, PSIG_164_CHR, PSIG_164_MINBB
-#define PSIG_CFG_16_3 16, 3, 1, 8, 32, 1, 4, 64, 8, 1
-#define PSIG_CFG_4_6 4, 6, 3, 4, 64, 1, 4, 64, 8, 1
+#ifndef PSIG_84_PF
+#define PSIG_84_PF 2
+#endif
+#ifndef PSIG_84_PB
+#define PSIG_84_PB 2
+#endif
+#define PSIG_CFG_8_4 8, 4, PSIG_84_PF, PSIG_84_DAF, PSIG_84_NTF, PSIG_84_MINBF, PSIG_84_PB, PSIG_84_DAB, PSIG_84_NTB, PSIG_84_CHR, PSIG_84_MINBB
+#define PSIG_CFG_16_4 16, 4, 2, PSIG_164_DAF, PSIG_164_NTF, PSIG_164_MINBF, 2, PSIG_164_DAB, PSIG_164_NTB, PSIG_164_CHR, PSIG_164_MINBB
+#define PSIG_CFG_16_3 16, 3, 1, 8, 32, 1, 1, 4, 64, 8, 1
+#define PSIG_CFG_4_6 4, 6, 3, 4, 64, 1, 3, 4, 64, 8, 1
 using Cfg_8_4 = Config<PSIG_CFG_8_4>;
 using Cfg_16_4 = Config<PSIG_CFG_16_4>;
 using Cfg_16_3 = Config<PSIG_CFG_16_3>;
@@ -906,8 +915,8 @@ bool tiled_supported(const PsigSigDesc &desc)
     bool one_block_per_unit = false;
     const bool known = dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
-        one_block_per_unit = Shape<C::D, C::N, C::P, C::DAF>::TPU == C::NTF &&
-                             Shape<C::D, C::N, C::P, C::DAB>::TPU == C::NTB;
+        one_block_per_unit = Shape<C::D, C::N, C::PF, C::DAF>::TPU == C::NTF &&
+                             Shape<C::D, C::N, C::PB, C::DAB>::TPU == C::NTB;
     });
     if (!known) return false;
     long long top_size = 0;
@@ -925,7 +934,7 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
     int rc = PSIG_ERR_UNSUPPORTED;
     dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
-        using S = Shape<C::D, C::N, C::P, C::DAF>;
+        using S = Shape<C::D, C::N, C::PF, C::DAF>;
         constexpr int PARTS = S::TPU / C::NTF;
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
@@ -941,11 +950,11 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
             kernel<<<(unsigned)blocks, C::NTF, smem, stream>>>(path, out, desc.L, W, win, vec, words, (int)top_size);
         };
         if (projected) {
-            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, true, true>);
-            else launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, true, false>);
+            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, true>);
+            else launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, false>);
         } else {
-            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, false, true>);
-            else launch(sig_forward_tiled<C::D, C::N, C::P, C::DAF, C::NTF, C::MINBF, false, false>);
+            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, true>);
+            else launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, false>);
         }
         rc = check_launch();
     });
@@ -964,8 +973,8 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
     int rc = PSIG_ERR_UNSUPPORTED;
     dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
-        using S = Shape<C::D, C::N, C::P, C::DAB>;
-        using SM = BackwardSmem<C::D, C::N, C::P, C::DAB, C::NTB, C::CHR>;
+        using S = Shape<C::D, C::N, C::PB, C::DAB>;
+        using SM = BackwardSmem<C::D, C::N, C::PB, C::DAB, C::NTB, C::CHR>;
         constexpr int PARTS = S::TPU / C::NTB;
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
@@ -981,7 +990,7 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
             const size_t need = sizeof(float) * ((size_t)SM::Q * C::CHR * C::D + (size_t)ipow(C::D, C::N));
             if (need > smem) smem = need;
         }
-        auto kernel = sig_backward_tiled<C::D, C::N, C::P, C::DAB, C::NTB, C::CHR, C::MINBB>;
+        auto kernel = sig_backward_tiled<C::D, C::N, C::PB, C::DAB, C::NTB, C::CHR, C::MINBB>;
         if (smem > 48 * 1024) {
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
                 rc = PSIG_ERR_CUDA; return;
