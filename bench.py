@@ -328,11 +328,12 @@ def time_steps(fn, steps, warmup, world, device):
     return _max_over_ranks(start.elapsed_time(end), world, device)
 
 
-def measure_fp32_peak(device):
-    """TFLOP/s of a register-only FFMA loop (psig_probe_fp32_fma), best of 5."""
+def measure_fp32_peak(device, packed=False):
+    """TFLOP/s of a register-only FFMA loop (psig_probe_fp32_fma[_packed]), best of 5."""
     import ctypes
     from pathsig_b200 import _load
     lib = _load.ensure_loaded()
+    probe = lib.psig_probe_fp32_fma_packed if packed else lib.psig_probe_fp32_fma
     scratch = torch.zeros(16, device=device)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -340,7 +341,7 @@ def measure_fp32_peak(device):
     for it in range(6):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        fmas = lib.psig_probe_fp32_fma(sms * 8, 20000, ctypes.c_void_p(scratch.data_ptr()), stream)
+        fmas = probe(sms * 8, 20000, ctypes.c_void_p(scratch.data_ptr()), stream)
         e.record()
         torch.cuda.synchronize()
         if it > 0:
@@ -574,6 +575,7 @@ def run_ours(args):
         print(json.dumps({"profile_run": args.workload, "batch": wl.B, "passes": args.warmup + args.steps}))
         return
     fp32_peak = measure_fp32_peak(device)
+    fp32_peak_packed = measure_fp32_peak(device, packed=True)
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -643,6 +645,7 @@ def run_ours(args):
             "bound": "fp32_fma", "kernel": "signature_backward operator (cudaMemsetAsync of grad_path + sig_backward_tiled)",
             "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
             "peak_source": "psig_probe_fp32_fma measured in this process (MEASURED_PEAKS.json has no FP32 figure)",
+            "peak_packed_fma": fp32_peak_packed,
             "flop_per_launch": bwd_flop, "flop_convention": "backward credited 3 x F_fwd FMAs per path*step",
             "traffic": NCU_TRAFFIC_BYTES.get(name),
             "whole_step": {"achieved": main["tflops_fwd_bwd"], "frac": main["tflops_fwd_bwd"] / (fp32_peak * world)},

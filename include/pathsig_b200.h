@@ -151,6 +151,8 @@ int64_t psig_sig_backward_static_limit(void);
  * FMAs issued (or a negative PsigStatus).  Timed by the caller, it gives the FP32 FMA peak used
  * as the roofline denominator.  `scratch` must point to at least 4 bytes of device memory. */
 int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream);
+/* The same loop issued as packed two-lane FMAs (fma.rn.f32x2); same FMA count returned. */
+int64_t psig_probe_fp32_fma_packed(int blocks, int iters, void *scratch, void *stream);
 
 #ifdef __cplusplus
 }

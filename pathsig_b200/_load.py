@@ -70,6 +70,7 @@ EXPORTS = {
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "psig_probe_fp32_fma": (_i64, [_int, _int, _vp, _vp]),
+    "psig_probe_fp32_fma_packed": (_i64, [_int, _int, _vp, _vp]),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),
     "psig_sig_backward_static_limit": (_i64, []),
 }

@@ -2,8 +2,6 @@
 // the device it runs on (the roofline denominator of the signature kernels).
 #include "common.cuh"
 
-#include <cstdlib>
-
 namespace psig {
 namespace {
 
@@ -51,12 +49,17 @@ __global__ void __launch_bounds__(256) ffma2_probe(float *out, int iters, float 
 extern "C" int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream)
 {
     if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
-    if (iters < 0x40000000 && getenv("PSIG_PROBE_PACKED"))  // experiment switch: packed f32x2 variant
-        psig::ffma2_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
-                                                                               0.999999f, 1e-7f);
-    else
     psig::ffma_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
                                                                           0.999999f, 1e-7f);
     if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
     return (int64_t)blocks * 256 * (int64_t)iters * 8 * 16;  // FMAs issued
+}
+
+extern "C" int64_t psig_probe_fp32_fma_packed(int blocks, int iters, void *scratch, void *stream)
+{
+    if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
+    psig::ffma2_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
+                                                                           0.999999f, 1e-7f);
+    if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    return (int64_t)blocks * 256 * (int64_t)iters * 8 * 16;  // FMAs issued (two per packed instruction)
 }

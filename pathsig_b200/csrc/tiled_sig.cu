@@ -859,7 +859,28 @@ struct Config {
 #define PSIG_CFG_8_4 8, 4, PSIG_84_PF, PSIG_84_DAF, PSIG_84_NTF, PSIG_84_MINBF, PSIG_84_PB, PSIG_84_DAB, PSIG_84_NTB, PSIG_84_CHR, PSIG_84_MINBB
 #define PSIG_CFG_16_4 16, 4, 2, PSIG_164_DAF, PSIG_164_NTF, PSIG_164_MINBF, 2, PSIG_164_DAB, PSIG_164_NTB, PSIG_164_CHR, PSIG_164_MINBB
 #define PSIG_CFG_16_3 16, 3, 1, 8, 32, 1, 1, 4, 64, 8, 1
-#define PSIG_CFG_4_6 4, 6, 3, 4, 64, 1, 3, 4, 64, 8, 1
+#ifndef PSIG_46_DAF
+#define PSIG_46_DAF 4
+#endif
+#ifndef PSIG_46_NTF
+#define PSIG_46_NTF 64
+#endif
+#ifndef PSIG_46_MINBF
+#define PSIG_46_MINBF 1
+#endif
+#ifndef PSIG_46_DAB
+#define PSIG_46_DAB 4
+#endif
+#ifndef PSIG_46_NTB
+#define PSIG_46_NTB 64
+#endif
+#ifndef PSIG_46_CHR
+#define PSIG_46_CHR 8
+#endif
+#ifndef PSIG_46_MINBB
+#define PSIG_46_MINBB 1
+#endif
+#define PSIG_CFG_4_6 4, 6, 3, PSIG_46_DAF, PSIG_46_NTF, PSIG_46_MINBF, 3, PSIG_46_DAB, PSIG_46_NTB, PSIG_46_CHR, PSIG_46_MINBB
 using Cfg_8_4 = Config<PSIG_CFG_8_4>;
 using Cfg_16_4 = Config<PSIG_CFG_16_4>;
 using Cfg_16_3 = Config<PSIG_CFG_16_3>;
