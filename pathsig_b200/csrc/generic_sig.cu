@@ -112,8 +112,9 @@ __device__ __forceinline__ void unit_window(const GenericPlan &p, long long unit
     start = 0;
     int end = (int)p.L;
     if (p.windows) {
-        start = p.windows[2 * w];
-        end = p.windows[2 * w + 1];
+        // clamped to the path: a window reaching outside reads only the points that exist
+        start = max(p.windows[2 * w], 0);
+        end = min(p.windows[2 * w + 1], (int)p.L);
     }
     steps = max(end - start - 1, 0);
 }

@@ -104,8 +104,9 @@ __device__ __forceinline__ void window_of(long long unit, long long L, long long
     int end = (int)L;
     if (windows) {
         const long long w = unit % W;
-        start = windows[2 * w];
-        end = windows[2 * w + 1];
+        // clamped to the path: a window reaching outside reads only the points that exist
+        start = max(windows[2 * w], 0);
+        end = min(windows[2 * w + 1], (int)L);
     }
     steps = max(end - start - 1, 0);
 }

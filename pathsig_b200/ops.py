@@ -173,6 +173,8 @@ def _compute_signature_cuda(path_in, depth, alternative_projection, encoded_word
     D = _row_width(desc.d, desc.depth, bool(alternative_projection), level_sizes)
     shape = (desc.B, desc.W, D) if use_windows else (desc.B, D)
     out = torch.empty(shape, dtype=path.dtype, device=path.device)
+    if out.numel() == 0:  # no paths, no windows or no requested words: nothing to launch
+        return out
     with torch.cuda.device(path.device):
         rc = lib.psig_sig_forward(ctypes.byref(desc), _ptr(path), _ptr(out), _stream_ptr(path.device))
     _load.check(rc, "compute_signature")
@@ -203,6 +205,8 @@ def _signature_backward_cuda(path_in, signature_in, grad_signature_in, depth, al
         if use_windows and sig.dim() == 3 and sig.size(1) != desc.W:
             raise RuntimeError("windows.size(0) must match signature num_windows")
         raise RuntimeError("signature must be [B,S] or [B,W,S]")
+    if sig.numel() == 0:  # an empty signature carries no gradient
+        return torch.zeros_like(path)
     grad_path = torch.empty_like(path)
     with torch.cuda.device(path.device):
         ws_bytes = lib.psig_sig_backward_workspace(ctypes.byref(desc))

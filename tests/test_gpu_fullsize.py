@@ -21,6 +21,12 @@ from . import util
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 TOL = 1e-5
+# Input gradients at full length, float32 against a float64 oracle: both this library and the
+# reference roll the prefix signatures back over hundreds of steps in float32, which leaves
+# 3e-6 .. 1e-5 of the largest gradient entry depending on the row (measured), so the bound for
+# these long float32 sweeps is looser than for the signature itself.  (The reference's own
+# float32 gradient tolerances are 1e-4 and 1e-3: tests/test_sig.py:26-34, tests/test_logsig.py:24-31.)
+GRAD_TOL = 3e-5
 
 
 @pytest.fixture(scope="module")
@@ -63,7 +69,7 @@ def test_config1_full_against_oracle(ps, oracle):
     want = oracle.sig_forward(x64, 4)
     assert max(util.level_rel_errors(out, want, util.level_widths(8, 4))) < TOL
     want_grad = oracle.sig_backward(x64, want, wl.G.double().cpu(), 4)
-    assert util.rel_error(grad, want_grad) < TOL
+    assert util.rel_error(grad, want_grad) < GRAD_TOL
     _check_translation_invariance(grad)
 
 
@@ -80,7 +86,7 @@ def test_config2_full(ps, oracle):
     want = oracle.sig_forward(x64, 4, windows=wl.windows)
     assert max(util.level_rel_errors(out[rows], want, util.level_widths(8, 4))) < TOL
     want_grad = oracle.sig_backward(x64, want, wl.G[rows].double().cpu(), 4, windows=wl.windows)
-    assert util.rel_error(grad[rows], want_grad) < TOL
+    assert util.rel_error(grad[rows], want_grad) < GRAD_TOL
     # the generic kernels on a slice of the batch
     ps.ops.set_algorithm("generic")
     try:
@@ -90,7 +96,7 @@ def test_config2_full(ps, oracle):
         ps.ops.set_algorithm("auto")
     out_t, grad_t = _fwd_bwd(small)
     assert max(util.level_rel_errors(out_t, out_g, util.level_widths(8, 4))) < TOL
-    assert util.rel_error(grad_t, grad_g) < TOL
+    assert util.rel_error(grad_t, grad_g) < GRAD_TOL
 
 
 def test_config3_full(ps, oracle):
@@ -106,7 +112,7 @@ def test_config3_full(ps, oracle):
     want = oracle.sig_forward(x64, 6, proj.encoded_words.cpu(), proj.level_sizes)
     assert max(util.level_rel_errors(out[rows], want, util.level_widths(8, 6, proj.level_sizes))) < TOL
     want_grad = oracle.sig_backward(x64, want, wl.G[rows].double().cpu(), 6, proj.encoded_words.cpu(), proj.level_sizes)
-    assert util.rel_error(grad[rows], want_grad) < TOL
+    assert util.rel_error(grad[rows], want_grad) < GRAD_TOL
 
 
 def test_config4_full(ps, oracle):
@@ -122,7 +128,7 @@ def test_config4_full(ps, oracle):
                                           ext_level_sizes=mod._ext_level_sizes, indices=mod._indices_from_sig.cpu(),
                                           grad_out=wl.G[rows].double().cpu())
     assert util.rel_error(out[rows], want) < TOL
-    assert util.rel_error(grad[rows], want_grad) < TOL
+    assert util.rel_error(grad[rows], want_grad) < GRAD_TOL
 
 
 def test_config5_shard(ps, oracle):
@@ -145,4 +151,4 @@ def test_config5_shard(ps, oracle):
     want = oracle.sig_forward(x64, 4)
     assert max(util.level_rel_errors(out[:2], want, util.level_widths(16, 4))) < TOL
     want_grad = oracle.sig_backward(x64[:1], want[:1], wl.G[:1].double().cpu(), 4)
-    assert util.rel_error(grad[:1], want_grad) < TOL
+    assert util.rel_error(grad[:1], want_grad) < GRAD_TOL

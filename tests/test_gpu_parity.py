@@ -145,6 +145,26 @@ def test_zero_batch_and_errors(ps):
         ps.Signature(depth=2, windows=torch.zeros(3, 2, dtype=torch.int32))  # CPU windows
 
 
+def test_empty_and_out_of_range_windows(ps, oracle):
+    x = util.brownian_path(2, 12, 3, seed=1, dtype=torch.float64)
+    none = torch.empty((0, 2), dtype=torch.int32, device=DEV)
+    xg = x.to(DEV).requires_grad_(True)
+    out = ps.Signature(depth=2, windows=none)(xg)
+    assert out.shape == (2, 0, 12)
+    out.sum().backward()
+    assert torch.all(xg.grad == 0)
+    # a window reaching past the end is clamped to the points that exist
+    win = torch.tensor([[8, 20], [-3, 5]], dtype=torch.int32, device=DEV)
+    got = ps.Signature(depth=2, windows=win)(x.to(DEV))
+    assert util.rel_error(got[:, 0], oracle.sig_forward(x[:, 8:12], 2)) < 1e-12
+    assert util.rel_error(got[:, 1], oracle.sig_forward(x[:, 0:5], 2)) < 1e-12
+    x32 = util.brownian_path(2, 40, 8, seed=2, dtype=torch.float32)
+    win = torch.tensor([[30, 99]], dtype=torch.int32, device=DEV)
+    got = ps.Signature(depth=4, windows=win)(x32.to(DEV))  # tiled kernels
+    want = oracle.sig_forward(x32[:, 30:40].double(), 4)
+    assert max(util.level_rel_errors(got[:, 0], want, util.level_widths(8, 4))) < 1e-5
+
+
 def test_non_contiguous_input_and_inference_mode(ps, oracle):
     x = util.brownian_path(4, 20, 6, seed=2, dtype=torch.float64)
     xt = x.to(DEV).transpose(0, 1).contiguous().transpose(0, 1)  # non-contiguous view, same values
