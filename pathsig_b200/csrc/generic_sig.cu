@@ -28,6 +28,8 @@ namespace {
 constexpr int kBlock = 128;
 constexpr size_t kStageBytes = 24 * 1024;
 constexpr size_t kSlotBytes = 44 * 1024;
+constexpr size_t kLaneBytes = 40 * 1024;   // staged increments (and gradients) of 32 units per block
+constexpr long long kLaneMaxItems = 1024;  // above this the item-per-thread kernels fill their warps anyway
 
 struct GenericPlan {
     LevelTable lt;
@@ -36,6 +38,10 @@ struct GenericPlan {
     int tiles;                            // letter tiles per dense prefix
     int chunk;                            // steps staged per refill
     int slot_stride;                      // backward: scalars per private gradient slot (0 = shared atomics)
+    // "one lane per unit" kernels: items numbered without padding, 32 units per block
+    long long lane_start[kMaxDepth + 2];  // first item of each degree; [depth+1] = total
+    int lane_chunk;                       // steps staged per refill (0 = lane kernels not used)
+    int lane_stride;                      // scalars between two units' rows of staged increments (odd)
     long long B, L, W;                    // W >= 1
     const int *windows;
 };
@@ -70,14 +76,14 @@ struct Item {
 };
 
 template <int TB>
-__device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi)
+__device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi, const long long *first)
 {
     Item it{1, 0, 0, 0, 0};
-    if (gi >= p.item_start[p.lt.depth + 1]) return it;
+    if (gi >= first[p.lt.depth + 1]) return it;
     int K = 1;
-    while (K < p.lt.depth && gi >= p.item_start[K + 1]) ++K;
+    while (K < p.lt.depth && gi >= first[K + 1]) ++K;
     it.K = K;
-    it.idx = gi - p.item_start[K];
+    it.idx = gi - first[K];
     if (it.idx >= p.items[K]) return it;  // padding between degrees
     const int d = p.lt.d;
     if (p.lt.words[K] == nullptr) {
@@ -253,7 +259,7 @@ __global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T *s_dx = reinterpret_cast<T *>(smem_raw);
     const int d = p.lt.d;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kBlock + threadIdx.x);
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kBlock + threadIdx.x, p.item_start);
     int let[kMaxDepth];
     prefix_letters(it, d, let);
     const long long units = p.B * p.W;
@@ -303,7 +309,7 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
     T *s_gd = s_dx + (size_t)p.chunk * p.lt.d;
     const int d = p.lt.d;
     const long long block_first = (long long)blockIdx.x * kBlock;
-    const Item it = decode_item<TB>(p, block_first + threadIdx.x);
+    const Item it = decode_item<TB>(p, block_first + threadIdx.x, p.item_start);
     int let[kMaxDepth];
     prefix_letters(it, d, let);
     const bool slots = p.slot_stride > 0;
@@ -404,6 +410,221 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// "One lane per unit" kernels.  When a row has few items (a projection onto a few hundred words,
+// or a small dense signature) but the batch has many units, the item-per-thread layout above
+// leaves most lanes idle.  Here a warp takes ONE item and its 32 lanes take 32 different
+// (path, window) units: every lane runs the same chain on its own unit's increments, so there is
+// no divergence and no idle lane, and a block of kLaneWarps warps shares one staging of the 32
+// units' increments.  Same step functions, same arithmetic.
+// ------------------------------------------------------------------------------------------
+#ifndef PSIG_LANE_WARPS
+#define PSIG_LANE_WARPS 16
+#endif
+constexpr int kLaneWarps = PSIG_LANE_WARPS;
+constexpr int kLaneBlock = 32 * kLaneWarps;
+
+struct LaneUnit {  // per-unit facts, published once per unit group in shared memory
+    long long b;
+    int start, steps;
+};
+
+__device__ __forceinline__ void publish_units(const GenericPlan &p, long long group, LaneUnit *s_unit)
+{
+    if (threadIdx.x < 32) {
+        const long long unit = group * 32 + threadIdx.x;
+        LaneUnit lu{0, 0, 0};
+        if (unit < p.B * p.W) unit_window(p, unit, lu.b, lu.start, lu.steps);
+        s_unit[threadIdx.x] = lu;
+    }
+}
+
+// s_dx[r * stride + t * d + a] = increment c0+t of unit r (r = 0..31), zero beyond its last step.
+// Each warp takes whole units: coalesced reads along the unit's row, independent loads in flight.
+template <typename T>
+__device__ __forceinline__ void stage_unit_increments(const GenericPlan &p, const T *__restrict__ path,
+                                                      const LaneUnit *s_unit, int c0, int n, T *s_dx)
+{
+    const int d = p.lt.d, row = n * d, lane = threadIdx.x & 31;
+    for (int r = threadIdx.x >> 5; r < 32; r += kLaneWarps) {
+        const LaneUnit lu = s_unit[r];
+        const T *lo = path + (lu.b * p.L + lu.start + c0) * d;
+        const int valid = max(0, min(n, lu.steps - c0)) * d;
+        T *dst = s_dx + r * p.lane_stride;
+        if constexpr (sizeof(T) == 4) {
+            // 128-bit loads when rows are 16-byte aligned (d a multiple of 4, aligned base pointer)
+            if ((d & 3) == 0 && (reinterpret_cast<uintptr_t>(lo) & 15u) == 0) {
+#pragma unroll 2
+                for (int j = 4 * lane; j < row; j += 128) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j < valid) {
+                        const float4 a = *reinterpret_cast<const float4 *>(lo + j);
+                        const float4 c = *reinterpret_cast<const float4 *>(lo + j + d);
+                        v = make_float4(c.x - a.x, c.y - a.y, c.z - a.z, c.w - a.w);
+                    }
+                    dst[j] = v.x; dst[j + 1] = v.y; dst[j + 2] = v.z; dst[j + 3] = v.w;
+                }
+                continue;
+            }
+        }
+#pragma unroll 4
+        for (int j = lane; j < row; j += 32) dst[j] = (j < valid) ? lo[j + d] - lo[j] : T(0);
+    }
+}
+
+template <typename T, int TB>
+__global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPlan p, const T *__restrict__ path,
+                                                                T *__restrict__ out)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *s_dx = reinterpret_cast<T *>(smem_raw);
+    __shared__ LaneUnit s_unit[32];
+    const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start);
+    int let[kMaxDepth];
+    prefix_letters(it, d, let);
+    const long long units = p.B * p.W, groups = (units + 31) / 32;
+
+    for (long long group = blockIdx.y; group < groups; group += gridDim.y) {
+        __syncthreads();
+        publish_units(p, group, s_unit);
+        __syncthreads();
+        const int steps = s_unit[lane].steps;
+        int max_steps = 0;
+        for (int r = 0; r < 32; ++r) max_steps = max(max_steps, s_unit[r].steps);
+
+        T pref[kMaxDepth], cpref[kMaxDepth], top[TB], ctop[TB];
+#pragma unroll
+        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); cpref[j] = T(0); }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) { top[i] = T(0); ctop[i] = T(0); }
+
+        for (int c0 = 0; c0 < max_steps; c0 += p.lane_chunk) {
+            const int n = min(p.lane_chunk, max_steps - c0);
+            __syncthreads();
+            stage_unit_increments(p, path, s_unit, c0, n, s_dx);
+            __syncthreads();
+            if (it.nb == 0) continue;
+            const T *mine = s_dx + lane * p.lane_stride;
+            const int n_lane = min(n, steps - c0);  // steps of this lane's unit inside the chunk
+            PSIG_SWITCH_DEGREE(it.K, {
+                for (int t = 0; t < n_lane; ++t) forward_step<T, K, TB>(mine + t * d, let, it, pref, cpref, top, ctop);
+            });
+        }
+        const long long unit = group * 32 + lane;
+        if (it.nb == 0 || unit >= units) continue;
+        T *row = out + unit * p.lt.total + p.lt.offset[it.K];
+        if (p.lt.words[it.K] == nullptr) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i)
+                if (i < it.nb) row[it.u * d + it.b0 + i] = top[i];
+        } else {
+            row[it.idx] = top[0];
+        }
+    }
+}
+
+template <typename T, int TB>
+__global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPlan p, const T *__restrict__ path,
+                                                                 const T *__restrict__ sig,
+                                                                 const T *__restrict__ grad,
+                                                                 T *__restrict__ inc_grad)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *s_dx = reinterpret_cast<T *>(smem_raw);
+    T *s_gd = s_dx + 32 * (size_t)p.lane_stride;
+    __shared__ LaneUnit s_unit[32];
+    const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start);
+    int let[kMaxDepth];
+    prefix_letters(it, d, let);
+    const bool rebuild = it.nb > 0 && !p.lt.lower_dense[it.K];
+    const bool any_rebuild = __syncthreads_or(rebuild ? 1 : 0) != 0;
+    const long long units = p.B * p.W, groups = (units + 31) / 32;
+
+    for (long long group = blockIdx.y; group < groups; group += gridDim.y) {
+        __syncthreads();
+        publish_units(p, group, s_unit);
+        __syncthreads();
+        const long long unit = group * 32 + lane;
+        const bool live = it.nb > 0 && unit < units;
+        const int steps = s_unit[lane].steps;
+        int max_steps = 0;
+        for (int r = 0; r < 32; ++r) max_steps = max(max_steps, s_unit[r].steps);
+        if (max_steps == 0) continue;  // uniform over the block
+
+        T pref[kMaxDepth], apref[kMaxDepth], g[TB];
+#pragma unroll
+        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); apref[j] = T(0); }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) g[i] = T(0);
+        if (live) {
+            const T *grow = grad + unit * p.lt.total + p.lt.offset[it.K];
+            if (p.lt.words[it.K] == nullptr) {
+#pragma unroll
+                for (int i = 0; i < TB; ++i)
+                    if (i < it.nb) g[i] = grow[it.u * d + it.b0 + i];
+            } else {
+                g[0] = grow[it.idx];
+            }
+            if (!rebuild) {
+                const T *srow = sig + unit * p.lt.total;
+                long long c = it.u;
+#pragma unroll
+                for (int j = kMaxDepth - 1; j >= 1; --j)
+                    if (j <= it.K - 1) { pref[j] = srow[p.lt.dense_offset[j] + c]; c /= d; }
+            }
+        }
+        if (any_rebuild) {
+            for (int c0 = 0; c0 < max_steps; c0 += p.lane_chunk) {
+                const int n = min(p.lane_chunk, max_steps - c0);
+                __syncthreads();
+                stage_unit_increments(p, path, s_unit, c0, n, s_dx);
+                __syncthreads();
+                if (!rebuild || !live) continue;
+                const T *mine = s_dx + lane * p.lane_stride;
+                const int n_lane = min(n, steps - c0);
+                PSIG_SWITCH_DEGREE(it.K, {
+                    for (int t = 0; t < n_lane; ++t) prefix_step<T, K>(mine + t * d, let, pref);
+                });
+            }
+        }
+
+        const int nchunks = (max_steps + p.lane_chunk - 1) / p.lane_chunk;
+        for (int ci = nchunks - 1; ci >= 0; --ci) {
+            const int c0 = ci * p.lane_chunk;
+            const int n = min(p.lane_chunk, max_steps - c0);
+            __syncthreads();
+            stage_unit_increments(p, path, s_unit, c0, n, s_dx);
+            for (int i = threadIdx.x; i < 32 * p.lane_stride; i += kLaneBlock) s_gd[i] = T(0);
+            __syncthreads();
+            if (live) {
+                const T *mine = s_dx + lane * p.lane_stride;
+                T *mine_gd = s_gd + lane * p.lane_stride;
+                const int n_lane = min(n, steps - c0);
+                PSIG_SWITCH_DEGREE(it.K, {
+                    for (int t = n_lane - 1; t >= 0; --t)
+                        backward_step<T, K, TB>(mine + t * d, let, it, pref, apref, g, mine_gd + t * d, false);
+                });
+            }
+            __syncthreads();
+            // flush the 32 units' rows of this chunk, one unit per warp at a time
+            const int row = n * d;
+            for (int r = warp; r < 32; r += kLaneWarps) {
+                const LaneUnit lu = s_unit[r];
+                T *dst = inc_grad + (lu.b * (p.L - 1) + lu.start + c0) * d;
+                const T *src = s_gd + r * p.lane_stride;
+                const int valid = max(0, min(n, lu.steps - c0)) * d;
+                for (int j = lane; j < valid; j += 32) {
+                    const T v = src[j];
+                    if (v != T(0)) atomicAdd(&dst[j], v);
+                }
+            }
+            (void)row;
+        }
+    }
+}
+
 // grad wrt increments -> grad wrt points (64-bit indexing).
 template <typename T>
 __global__ void increments_to_points(const T *__restrict__ inc_grad, T *__restrict__ path_grad, long long B,
@@ -455,6 +676,20 @@ int make_plan(const PsigSigDesc &desc, const LevelTable &lt, int buffers, Generi
     if (chunk < 1) chunk = 1;
     if (chunk > 64) chunk = 64;
     p.chunk = (int)chunk;
+    // lane kernels: worth it when rows have few items and there are at least a warp's worth of units
+    p.lane_chunk = 0;
+    p.lane_stride = 0;
+    long long lane_items = 0;
+    for (int k = 1; k <= lt.depth; ++k) { p.lane_start[k] = lane_items; lane_items += p.items[k]; }
+    for (int k = lt.depth + 1; k <= kMaxDepth + 1; ++k) p.lane_start[k] = lane_items;
+    {
+        const long long units = p.B * p.W;
+        const long long lane_steps = (long long)(kLaneBytes / (sizeof(T) * 32 * (size_t)lt.d * buffers));
+        if (units >= 32 && lane_items <= kLaneMaxItems && lane_steps >= 2) {
+            p.lane_chunk = (int)(lane_steps > 32 ? 32 : lane_steps);
+            p.lane_stride = (p.lane_chunk * lt.d) | 1;
+        }
+    }
     p.slot_stride = 0;
     if (buffers == 2) {
         // Backward with few channels: float atomics on a handful of shared addresses serialise, so
@@ -483,6 +718,14 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
     const long long units = plan.B * plan.W;
     const long long blocks = (plan.item_start[kMaxDepth + 1] + kBlock - 1) / kBlock;
     if (units == 0 || blocks == 0) return PSIG_OK;
+    if (plan.lane_chunk > 0) {
+        const long long groups = (units + 31) / 32;
+        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
+        const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
+        const size_t smem = sizeof(T) * 32 * (size_t)plan.lane_stride;
+        sig_forward_lanes<T, TB><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        return check_launch();
+    }
     const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
     const size_t smem = sizeof(T) * (size_t)plan.chunk * lt.d;
     sig_forward_generic<T, TB><<<grid, kBlock, smem, stream>>>(plan, path, out);
@@ -502,7 +745,14 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
     if (desc.B == 0) return PSIG_OK;
     const size_t inc_bytes = sizeof(T) * (size_t)desc.B * (size_t)(desc.L - 1) * lt.d;
     if (cudaMemsetAsync(inc_grad_ws, 0, inc_bytes, stream) != cudaSuccess) return PSIG_ERR_CUDA;
-    if (units > 0 && blocks > 0) {
+    if (units > 0 && blocks > 0 && plan.lane_chunk > 0) {
+        const long long groups = (units + 31) / 32;
+        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
+        const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
+        const size_t smem = 2 * sizeof(T) * 32 * (size_t)plan.lane_stride;
+        sig_backward_lanes<T, TB><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    } else if (units > 0 && blocks > 0) {
         const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
         const size_t smem = plan.slot_stride > 0
                                 ? sizeof(T) * (size_t)plan.chunk * ((size_t)lt.d + (size_t)kBlock * plan.slot_stride)

@@ -255,3 +255,22 @@ def test_lyndon_logsignature_float32_on_tiled_kernels(ps, oracle):
     want, want_grad = _oracle_logsig(oracle, mod, x.double(), g.double(), None)
     assert util.rel_error(out, want) < util.TOL[torch.float32]
     assert util.rel_error(xg.grad, want_grad) < util.TOL[torch.float32]
+
+
+# ---- batches of 32+ units: the generic "one lane per unit" kernels ----
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("d,depth", [(2, 5), (3, 4), (5, 3), (6, 2), (2, 12)])
+def test_many_units_dense(ps, oracle, dtype, d, depth):
+    x = util.brownian_path(45, 23, d, seed=d * depth, dtype=dtype)
+    _run_sig(ps, oracle, x, depth, algo="generic")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_many_units_ragged_windows_and_projection(ps, oracle, dtype):
+    x = util.brownian_path(9, 50, 4, seed=77, dtype=dtype)
+    win = torch.tensor([[0, 50], [5, 7], [10, 30], [3, 3], [12, 13], [20, 50], [0, 21], [44, 50]], dtype=torch.int32)
+    _run_sig(ps, oracle, x, 4, windows=win, algo="generic")                       # 72 units of unequal length
+    proj = ps.projections.words(util.random_words(70, 4, 1, 5, seed=8), 5, 4)
+    _run_sig(ps, oracle, x, 5, proj=proj, windows=win)
+    _run_sig(ps, oracle, util.brownian_path(64, 31, 4, seed=3, dtype=dtype), 5, proj=ps.projections.lyndon(5, 4))
