@@ -448,7 +448,7 @@ def run_reference(args):
         "note": "the reference has no CPU implementation (CUDA-only operators); this arm times the CPU "
                 "restatement of its algorithm (oracle/) on the host cores",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e2e=False, fp32_peak=None):
@@ -487,6 +487,24 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
         "hbm_gbs_fwd_bwd": wl.bytes_fwd_bwd * world / (ms_fb / steps * 1e-3) / 1e9,
         "kernels_per_step": wl.kernels_per_step(),
     })
+    if wl.units < 200000:
+        # launch-bound workload: the same forward+backward step captured in a CUDA graph and
+        # replayed (the operators enqueue on the current stream only, so capture is legal)
+        try:
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    wl.step_fwd_bwd()
+            torch.cuda.current_stream(device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                wl.step_fwd_bwd()
+            ms_g = time_steps(graph.replay, steps, warmup, world, device)
+            res["fwd_bwd_cuda_graph"] = {"value": total_units * steps / (ms_g * 1e-3), "ms_per_step": ms_g / steps}
+            del graph
+        except Exception as exc:  # reported, never fatal
+            res["fwd_bwd_cuda_graph"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:160]}
     if fp32_peak:
         res["frac_fp32_peak_fwd_bwd"] = res["tflops_fwd_bwd"] / (fp32_peak * world)
         res["frac_fp32_peak_fwd"] = res["tflops_fwd"] / (fp32_peak * world)
@@ -572,7 +590,7 @@ def run_ours(args):
         for _ in range(args.warmup + args.steps):
             wl.step_fwd_bwd()
         torch.cuda.synchronize()
-        print(json.dumps({"profile_run": args.workload, "batch": wl.B, "passes": args.warmup + args.steps}))
+        emit({"profile_run": args.workload, "batch": wl.B, "passes": args.warmup + args.steps})
         return
     fp32_peak_scalar = measure_fp32_peak(device)
     fp32_peak_packed = measure_fp32_peak(device, packed=True)
@@ -658,26 +676,27 @@ def run_ours(args):
         "reference_cuda": ref_cuda,
         "others": others,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_real_stdout = None
 
 
 def _claim_stdout():
-    """Keep stdout for the JSON line only: libraries (NCCL prints its version banner there) are
-    sent to stderr, and the returned file object writes to the real stdout."""
-    real = os.fdopen(os.dup(1), "w")
-    os.dup2(2, 1)
-    return real
+    """Keep stdout for the JSON line only: anything a library prints there (NCCL's version banner,
+    for one) goes to stderr instead; emit() writes to the real stdout."""
+    global _real_stdout
+    if _real_stdout is None:
+        _real_stdout = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    print(json.dumps(obj), file=_real_stdout or sys.stdout, flush=True)
 
 
 def main():
-    global print
-    real_stdout = _claim_stdout()
-    _print = print
-
-    def print(*a, **k):  # noqa: A001  (every print of this module goes to the real stdout)
-        k.setdefault("file", real_stdout)
-        _print(*a, **k)
-
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -48,7 +48,7 @@ typedef enum PsigStatus {
     PSIG_ERR_DTYPE = -2,       /* dtype is neither PSIG_F32 nor PSIG_F64 */
     PSIG_ERR_DEPTH = -3,       /* depth outside 1..12 */
     PSIG_ERR_SHAPE = -4,       /* B < 0, L < 2, d < 1, W < 0 or inconsistent level_sizes */
-    PSIG_ERR_PACKING = -5,     /* d needs more than 64/depth bits per letter */
+    PSIG_ERR_PACKING = -5,     /* d^depth does not fit a signed 64-bit word code */
     PSIG_ERR_WORKSPACE = -6,   /* workspace too small or NULL */
     PSIG_ERR_CUDA = -7,        /* a CUDA runtime call or launch failed (see cudaGetLastError) */
     PSIG_ERR_TOO_LARGE = -8,   /* a size exceeds what the entry point supports */
@@ -105,7 +105,8 @@ int64_t psig_logsig_size(const PsigLogDesc *desc);
  * Replaces pathsig::compute_signature (src/pathsig/forward/sig_launch.cu:75-225). */
 int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void *stream);
 
-/* Scratch bytes psig_sig_backward needs for this description (may be 0). */
+/* Scratch bytes psig_sig_backward needs for this description: 0 for the register-tiled kernels,
+ * sizeof(scalar)*B*(L-1)*d for the generic ones. */
 int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
 
 /* grad_path (B, L, d) = d/dpath of sum(signature * grad_sig).  `sig` is the forward output for
