@@ -837,7 +837,7 @@ struct Config {
 #define PSIG_164_NTF 128
 #endif
 #ifndef PSIG_164_MINBF
-#define PSIG_164_MINBF 1
+#define PSIG_164_MINBF 3
 #endif
 #ifndef PSIG_164_DAB
 #define PSIG_164_DAB 8
