@@ -111,8 +111,10 @@ __device__ __forceinline__ void window_of(long long unit, long long L, long long
     steps = max(end - start - 1, 0);
 }
 
-// s_dx[r][t][a] = dx_{c0+t}[a] / (r+1) for r < Q.
-template <int D, int Q, int CH, int NT>
+// s_dx[0][t][a] = dx_{c0+t}[a]; with HALF also s_dx[1][t][a] = dx_{c0+t}[a] / 2.  Elsewhere the 1/2 and
+// 1/3 factors of the Horner tail are applied to the scalar multiplier instead of to the vector; the
+// halved table is kept for the backward sweep with a two-level sub-tree, where it measured faster.
+template <int D, bool HALF, int CH, int NT>
 __device__ __forceinline__ void stage_scaled_increments(const float *__restrict__ x, int c0, int n,
                                                         float (*s_dx)[CH][D])
 {
@@ -120,8 +122,7 @@ __device__ __forceinline__ void stage_scaled_increments(const float *__restrict_
     for (int i = threadIdx.x; i < n * D; i += NT) {
         const float v = lo[i + D] - lo[i];
         (&s_dx[0][0][0])[i] = v;
-        if constexpr (Q >= 2) (&s_dx[1][0][0])[i] = v * 0.5f;
-        if constexpr (Q >= 3) (&s_dx[2][0][0])[i] = v * recip<float>(3);
+        if constexpr (HALF) (&s_dx[1][0][0])[i] = v * 0.5f;
     }
 }
 
@@ -188,14 +189,12 @@ __device__ __forceinline__ void pipe_issue(PointPipe<D, MAXPTS> &pp, int slot, c
 }
 
 // s_dx tables from staged points: raw[t*D + a], t = 0..n.
-template <int D, int Q, int CH, int NT>
+template <int D, int CH, int NT>
 __device__ __forceinline__ void scaled_increments_from_points(const float *raw, int n, float (*s_dx)[CH][D])
 {
     for (int i = threadIdx.x; i < n * D; i += NT) {
         const float v = raw[i + D] - raw[i];
         (&s_dx[0][0][0])[i] = v;
-        if constexpr (Q >= 2) (&s_dx[1][0][0])[i] = v * 0.5f;
-        if constexpr (Q >= 3) (&s_dx[2][0][0])[i] = v * recip<float>(3);
     }
 }
 
@@ -224,22 +223,26 @@ __device__ __forceinline__ void fma_pair(float &x0, float &x1, float a0, float a
 #endif
 }
 
+// Whether the backward sweep keeps a second table of halved increments.  Measured: with a two-level
+// sub-tree and few channels the table wins (about 3 % at d = 8); at d = 16 the registers it costs
+// lose more than the multiplications it saves.
+__host__ __device__ constexpr bool half_table(int D, int Q) { return Q == 2 && D <= 8; }
+
 // The operands one step needs: the increment at this thread's prefix letters, the full
 // increment vector, and the (scaled) slices at the owned first letters.
-template <int D, int DA, int P, int Q>
+template <int D, int DA, int P, bool HALF = false>
 struct StepOperands {
     float xs[P];
     float dxf1[D];                      // dx
     float dxa1[DA];                     // dx[a0..]
-    float dxa2[Q >= 2 ? DA : 1];        // dx[a0..] / 2
-    float dxa3[Q >= 3 ? DA : 1];        // dx[a0..] / 3
-    float dxf2[Q >= 3 ? D : 1];         // dx / 2
+    float dxa2[HALF ? DA : 1];          // dx[a0..] / 2
 };
 
-template <int D, int DA, int P, int Q, int CH, bool XS_GIVEN = false>
-__device__ __forceinline__ void load_operands(StepOperands<D, DA, P, Q> &o, const float (*s_dx)[CH][D], int t,
+template <int D, int DA, int P, bool HALF, int CH, bool XS_GIVEN = false>
+__device__ __forceinline__ void load_operands(StepOperands<D, DA, P, HALF> &o, const float (*s_dx)[CH][D], int t,
                                               const int (&let)[P], int a0)
 {
+    if constexpr (HALF) load_run<DA>(o.dxa2, s_dx[1][t] + a0, true);
     const float *row = s_dx[0][t];
     if constexpr (!XS_GIVEN) {
 #pragma unroll
@@ -251,11 +254,6 @@ __device__ __forceinline__ void load_operands(StepOperands<D, DA, P, Q> &o, cons
         for (int a = 0; a < DA; ++a) o.dxa1[a] = o.dxf1[a];
     } else {
         load_run<DA>(o.dxa1, row + a0, true);
-    }
-    if constexpr (Q >= 2) load_run<DA>(o.dxa2, s_dx[1][t] + a0, true);
-    if constexpr (Q >= 3) {
-        load_run<DA>(o.dxa3, s_dx[2][t] + a0, true);
-        load_run<D>(o.dxf2, s_dx[1][t], true);
     }
 }
 
@@ -275,7 +273,7 @@ struct ForwardState {
 };
 
 template <int D, int N, int P, int DA>
-__device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const StepOperands<D, DA, P, N - P> &o)
+__device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const StepOperands<D, DA, P> &o)
 {
     constexpr int Q = N - P;
     if constexpr (Q >= 3) {  // target degree P+3
@@ -283,12 +281,14 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
         float bb = 1.f;
 #pragma unroll
         for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
+        const float bb3 = bb * recip<float>(3);  // the stage's 1/3 rides on the scalar, not on the vector
 #pragma unroll
         for (int a = 0; a < DA; ++a) {
-            const float v1 = fmaf(bb, o.dxa3[a], s.R1[a]);
+            const float v1 = fmaf(bb3, o.dxa1[a], s.R1[a]);
+            const float v1h = 0.5f * v1;
 #pragma unroll
             for (int c = 0; c < D; ++c) {
-                const float v2 = fmaf(v1, o.dxf2[c], s.R2[a * D + c]);
+                const float v2 = fmaf(v1h, o.dxf1[c], s.R2[a * D + c]);
 #pragma unroll
                 for (int e = 0; e < D; e += 2)
                     fma_pair(s.R3[(a * D + c) * D + e], s.R3[(a * D + c) * D + e + 1], v2, v2, o.dxf1[e], o.dxf1[e + 1]);
@@ -300,9 +300,10 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
         float bb = 1.f;
 #pragma unroll
         for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
+        const float bbh = 0.5f * bb;
 #pragma unroll
         for (int a = 0; a < DA; ++a) {
-            const float v1 = fmaf(bb, o.dxa2[a], s.R1[a]);
+            const float v1 = fmaf(bbh, o.dxa1[a], s.R1[a]);
 #pragma unroll
             for (int c = 0; c < D; c += 2)
                 fma_pair(s.R2[a * D + c], s.R2[a * D + c + 1], v1, v1, o.dxf1[c], o.dxf1[c + 1]);
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     constexpr int Q = S::Q, PARTS = S::TPU / NT, CH = kFwdChunk;
     extern __shared__ __align__(16) float s_top[];  // D^N floats, only when the top degree is projected
     static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
-    __shared__ __align__(16) float s_dx[Q][CH][D];
+    __shared__ __align__(16) float s_dx[1][CH][D];
     __shared__ __align__(16) PointPipe<D, BULK ? CH + 1 : 1> s_pipe;  // one float per buffer when unused
 
     const long long unit = blockIdx.x / PARTS;
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
         for (int c0 = 0; c0 < steps; c0 += CH) {
             const int n = min(CH, steps - c0);
             block_sync<NT>();
-            stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+            stage_scaled_increments<D, false, CH, NT>(x, c0, n, s_dx);
             block_sync<NT>();
 #if PSIG_PREFETCH_XS_FWD
             float xs_next[P];
@@ -378,16 +379,16 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
 #endif
 #pragma unroll 1
             for (int t = 0; t < n; ++t) {
-                StepOperands<D, DA, P, Q> o;
+                StepOperands<D, DA, P> o;
 #if PSIG_PREFETCH_XS_FWD
 #pragma unroll
                 for (int j = 0; j < P; ++j) o.xs[j] = xs_next[j];
                 const int tn = min(t + 1, n - 1);
 #pragma unroll
                 for (int j = 0; j < P; ++j) xs_next[j] = s_dx[0][tn][let[j]];
-                load_operands<D, DA, P, Q, CH, true>(o, s_dx, t, let, a0);
+                load_operands<D, DA, P, false, CH, true>(o, s_dx, t, let, a0);
 #else
-                load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
+                load_operands<D, DA, P, false, CH>(o, s_dx, t, let, a0);
 #endif
                 forward_step<D, N, P, DA>(st, o);
             }
@@ -417,9 +418,9 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
                     issued = ci + 2;
                 }
                 if (!mbar_wait_bounded(&s_pipe.bar[ci & 1], (uint32_t)((ci >> 1) & 1))) s_pipe.failed = 1;
-                scaled_increments_from_points<D, Q, CH, NT>(s_pipe.raw[ci & 1], n, s_dx);
+                scaled_increments_from_points<D, CH, NT>(s_pipe.raw[ci & 1], n, s_dx);
             } else {
-                stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+                stage_scaled_increments<D, false, CH, NT>(x, c0, n, s_dx);
             }
             block_sync<NT>();
             if (bulk && s_pipe.failed) {
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
                 // later chunks with plain loads instead
                 if (threadIdx.x == 0) atomicAdd(&g_bulk_copy_timeouts, 1u);
                 bulk = false;
-                stage_scaled_increments<D, Q, CH, NT>(x, c0, n, s_dx);
+                stage_scaled_increments<D, false, CH, NT>(x, c0, n, s_dx);
                 block_sync<NT>();
             }
 #if PSIG_PREFETCH_XS_FWD
@@ -437,16 +438,16 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
 #endif
 #pragma unroll 1
             for (int t = 0; t < n; ++t) {
-                StepOperands<D, DA, P, Q> o;
+                StepOperands<D, DA, P> o;
 #if PSIG_PREFETCH_XS_FWD
 #pragma unroll
                 for (int j = 0; j < P; ++j) o.xs[j] = xs_next[j];
                 const int tn = min(t + 1, n - 1);
 #pragma unroll
                 for (int j = 0; j < P; ++j) xs_next[j] = s_dx[0][tn][let[j]];
-                load_operands<D, DA, P, Q, CH, true>(o, s_dx, t, let, a0);
+                load_operands<D, DA, P, false, CH, true>(o, s_dx, t, let, a0);
 #else
-                load_operands<D, DA, P, Q, CH>(o, s_dx, t, let, a0);
+                load_operands<D, DA, P, false, CH>(o, s_dx, t, let, a0);
 #endif
                 forward_step<D, N, P, DA>(st, o);
             }
@@ -531,7 +532,7 @@ __device__ __forceinline__ void head_chain(float (&bc)[P + 1], const float (&xs)
 // One reverse step.  On return gdf[e] / gda[a] / lg[j] hold this thread's share of dL/d(dx_t)
 // for letter e, for letter a0+a and for the prefix letter let[j].
 template <int D, int N, int P, int DA>
-__device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, const StepOperands<D, DA, P, N - P> &o,
+__device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, const StepOperands<D, DA, P, half_table(D, N - P)> &o,
                                               float (&gdf)[D], float (&gda)[DA], float (&lg)[P])
 {
     constexpr int Q = N - P;
@@ -580,10 +581,15 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
         float bc[P + 1];
         head_chain<P, k>(bc, o.xs, s.pref);
         const float bb = bc[P];
+        // the 1/2 of this stage comes with the halved table, or rides on the scalars
+        constexpr bool kTable = half_table(D, Q);
+        const float bbh = 0.5f * bb;
         float adj = 0.f;
 #pragma unroll
         for (int a = 0; a < DA; ++a) {
-            const float v1 = fmaf(bb, o.dxa2[a], s.RS1[a]);
+            float v1;
+            if constexpr (kTable) v1 = fmaf(bb, o.dxa2[a], s.RS1[a]);
+            else v1 = fmaf(bbh, o.dxa1[a], s.RS1[a]);
             float av_even = 0.f, av_odd = 0.f;
 #pragma unroll
             for (int c = 0; c < D; c += 2) {
@@ -595,24 +601,31 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
             }
             const float av = av_even + av_odd;
             s.RG1[a] += av;
-            adj = fmaf(av, o.dxa2[a], adj);
-            gda[a] = fmaf(av * 0.5f, bb, gda[a]);
+            if constexpr (kTable) {
+                adj = fmaf(av, o.dxa2[a], adj);
+                gda[a] = fmaf(av * 0.5f, bb, gda[a]);
+            } else {
+                adj = fmaf(av, o.dxa1[a], adj);
+                gda[a] = fmaf(av, bbh, gda[a]);
+            }
         }
-        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+        back_chain<P, k>(kTable ? adj : 0.5f * adj, bc, o.xs, s.apref, lg);
     }
     if constexpr (Q >= 3) {  // target degree P+3
         constexpr int k = P + 3;
         float bc[P + 1];
         head_chain<P, k>(bc, o.xs, s.pref);
         const float bb = bc[P];
+        const float bb3 = bb * recip<float>(3);  // stage factors 1/3 and 1/2 ride on the scalars
         float adj = 0.f;
 #pragma unroll
         for (int a = 0; a < DA; ++a) {
-            const float v1 = fmaf(bb, o.dxa3[a], s.RS1[a]);
+            const float v1 = fmaf(bb3, o.dxa1[a], s.RS1[a]);
+            const float v1h = 0.5f * v1;
             float av1 = 0.f;
 #pragma unroll
             for (int c = 0; c < D; ++c) {
-                const float v2 = fmaf(v1, o.dxf2[c], s.RS2[a * D + c]);
+                const float v2 = fmaf(v1h, o.dxf1[c], s.RS2[a * D + c]);
                 float av2_even = 0.f, av2_odd = 0.f;
 #pragma unroll
                 for (int e = 0; e < D; e += 2) {
@@ -622,14 +635,15 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
                 }
                 const float av2 = av2_even + av2_odd;
                 s.RG2[a * D + c] += av2;
-                av1 = fmaf(av2, o.dxf2[c], av1);
-                gdf[c] = fmaf(av2 * 0.5f, v1, gdf[c]);
+                av1 = fmaf(av2, o.dxf1[c], av1);      // adjoint of v1h, before the 1/2
+                gdf[c] = fmaf(av2, v1h, gdf[c]);
             }
+            av1 *= 0.5f;                               // adjoint of v1
             s.RG1[a] += av1;
-            adj = fmaf(av1, o.dxa3[a], adj);
-            gda[a] = fmaf(av1 * recip<float>(3), bb, gda[a]);
+            adj = fmaf(av1, o.dxa1[a], adj);
+            gda[a] = fmaf(av1, bb3, gda[a]);
         }
-        back_chain<P, k>(adj, bc, o.xs, s.apref, lg);
+        back_chain<P, k>(adj * recip<float>(3), bc, o.xs, s.apref, lg);
     }
 }
 
@@ -640,7 +654,9 @@ struct BackwardSmem {
     // stride of one slot fall into distinct banks.
     static constexpr int kSlot = D + 4;
     static constexpr int kPartRow = NT * kSlot;
-    static constexpr int kFloats = Q * CHR * D + CHR * kPartRow + (CHR + 1) * D;
+    static constexpr bool kHalf = half_table(D, Q);
+    static constexpr int kTables = kHalf ? 2 : 1;
+    static constexpr int kFloats = kTables * CHR * D + CHR * kPartRow + (CHR + 1) * D;
     static constexpr size_t kBytes = sizeof(float) * kFloats;
     // Block-wide sum of the partials: each group of kSlices adjacent lanes produces one float4
     // (4 letters of one step); used when the shape allows it, otherwise a scalar loop.
@@ -694,7 +710,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     static_assert(NT % 4 == 0, "block size must be a multiple of 4");
     extern __shared__ __align__(16) float smem[];
     float (*s_dx)[CHR][D] = reinterpret_cast<float (*)[CHR][D]>(smem);
-    float *s_part = smem + Q * CHR * D;
+    float *s_part = smem + SM::kTables * CHR * D;
     float *s_red = s_part + CHR * SM::kPartRow;  // rows 0..CHR-1: reduced dL/d(dx); row CHR: carry
 
     const long long unit = blockIdx.x / PARTS;
@@ -765,7 +781,7 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
         const int n = min(CHR, c_hi);
         const int c0 = c_hi - n;
         block_sync<NT>();
-        stage_scaled_increments<D, Q, CHR, NT>(x, c0, n, s_dx);
+        stage_scaled_increments<D, SM::kHalf, CHR, NT>(x, c0, n, s_dx);
         block_sync<NT>();
 
         float gdf[D], gda[DA], lg[P];
@@ -778,16 +794,16 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
 #endif
 #pragma unroll 1
         for (int t = n - 1; t >= 0; --t) {
-            StepOperands<D, DA, P, Q> o;
+            StepOperands<D, DA, P, SM::kHalf> o;
 #if PSIG_PREFETCH_XS_BWD
 #pragma unroll
             for (int j = 0; j < P; ++j) o.xs[j] = xs_next[j];
             const int tn = max(t - 1, 0);
 #pragma unroll
             for (int j = 0; j < P; ++j) xs_next[j] = s_dx[0][tn][let[j]];
-            load_operands<D, DA, P, Q, CHR, true>(o, s_dx, t, let, a0);
+            load_operands<D, DA, P, SM::kHalf, CHR, true>(o, s_dx, t, let, a0);
 #else
-            load_operands<D, DA, P, Q, CHR>(o, s_dx, t, let, a0);
+            load_operands<D, DA, P, SM::kHalf, CHR>(o, s_dx, t, let, a0);
 #endif
             backward_step<D, N, P, DA>(st, o, gdf, gda, lg);
             publish_partials<D, DA, P>(s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot, gdf, gda, lg, let, split);
@@ -1063,7 +1079,7 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
         // the projected-top prologue stages D^N floats in the partials area
         size_t smem = SM::kBytes;
         if (projected) {
-            const size_t need = sizeof(float) * ((size_t)SM::Q * C::CHR * C::D + (size_t)ipow(C::D, C::N));
+            const size_t need = sizeof(float) * ((size_t)SM::kTables * C::CHR * C::D + (size_t)ipow(C::D, C::N));
             if (need > smem) smem = need;
         }
         auto kernel = sig_backward_tiled<C::D, C::N, C::PB, C::DAB, C::NTB, C::CHR, C::MINBB>;
