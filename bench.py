@@ -542,7 +542,7 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
             cur.wait_event(ev_in[k % 2])
             x = xd[k % 2].detach().requires_grad_(True)
             out = wl.mod(x)
-            loss = (out * wl.G).sum()
+            loss = torch.dot(out.reshape(-1), wl.G.reshape(-1))
             loss.backward()
             gd[k % 2].copy_(x.grad)
             ld[k % 2].copy_(loss.detach().reshape(1))
@@ -572,7 +572,7 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
         res["e2e"] = {"value": total_units * steps / (ms_e * 1e-3), "unit": UNIT,
                       "h2d_bytes_per_step": xh.numel() * 4 * world, "d2h_bytes_per_step": (gh.numel() + 1) * 4 * world,
                       "ms_per_step": ms_e / steps,
-                      "api": "pathsig_b200.Signature(...)(x); (out*G).sum().backward(); every step copies its batch "
+                      "api": "pathsig_b200.Signature(...)(x); torch.dot(out.flatten(), G.flatten()).backward(); every step copies its batch "
                              "from pinned host memory and its grad and loss back, on a copy stream overlapped with "
                              "the neighbouring steps' compute (one extra batch is staged ahead)"}
     return res

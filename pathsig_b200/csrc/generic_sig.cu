@@ -40,6 +40,9 @@ struct GenericPlan {
     int slot_stride;                      // backward: scalars per private gradient slot (0 = shared atomics)
     // "one lane per unit" kernels: items numbered without padding, 32 units per block
     long long lane_start[kMaxDepth + 2];  // first item of each degree; [depth+1] = total
+    long long lane_items[kMaxDepth + 1];  // items per degree with tiles of lane_tb letters
+    int lane_tb;                          // letters per dense tile in the lane kernels (1 or tile_letters)
+    int lane_tiles;                       // letter tiles per dense prefix in the lane kernels
     int lane_chunk;                       // steps staged per refill (0 = lane kernels not used)
     int lane_stride;                      // scalars between two units' rows of staged increments (odd)
     long long B, L, W;                    // W >= 1
@@ -76,7 +79,8 @@ struct Item {
 };
 
 template <int TB>
-__device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi, const long long *first)
+__device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi, const long long *first,
+                                            const long long *items, int tiles)
 {
     Item it{1, 0, 0, 0, 0};
     if (gi >= first[p.lt.depth + 1]) return it;
@@ -84,11 +88,11 @@ __device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi, 
     while (K < p.lt.depth && gi >= first[K + 1]) ++K;
     it.K = K;
     it.idx = gi - first[K];
-    if (it.idx >= p.items[K]) return it;  // padding between degrees
+    if (it.idx >= items[K]) return it;  // padding between degrees
     const int d = p.lt.d;
     if (p.lt.words[K] == nullptr) {
-        it.u = it.idx / p.tiles;
-        it.b0 = (int)(it.idx % p.tiles) * TB;
+        it.u = it.idx / tiles;
+        it.b0 = (int)(it.idx % tiles) * TB;
         it.nb = min(TB, d - it.b0);
     } else {
         const long long code = p.lt.words[K][it.idx];
@@ -99,16 +103,18 @@ __device__ __forceinline__ Item decode_item(const GenericPlan &p, long long gi, 
     return it;
 }
 
-// Letters of the prefix, first letter in let[0]; entries at and beyond K-1 are zero.
-__device__ __forceinline__ void prefix_letters(const Item &it, int d, int (&let)[kMaxDepth])
+// Letters of the prefix, first letter in let[0]; entries at and beyond K-1 are zero.  MK bounds the
+// degree a kernel instance handles and sizes its per-thread arrays.
+template <int MK>
+__device__ __forceinline__ void prefix_letters(const Item &it, int d, int (&let)[MK])
 {
     long long c = it.u;
 #pragma unroll
-    for (int j = kMaxDepth - 2; j >= 0; --j) {
+    for (int j = MK - 2; j >= 0; --j) {
         let[j] = 0;
         if (j < it.K - 1) { let[j] = (int)(c % d); c /= d; }
     }
-    let[kMaxDepth - 1] = 0;
+    let[MK - 1] = 0;
 }
 
 __device__ __forceinline__ void unit_window(const GenericPlan &p, long long unit, long long &b, int &start, int &steps)
@@ -134,9 +140,9 @@ __device__ __forceinline__ void stage_increments(const T *__restrict__ x, int d,
 }
 
 // ---- one forward step of an item of degree K (pref[j] = S(u[:j]), top[i] = S(u.b_i)) ----
-template <typename T, int K, int TB>
-__device__ __forceinline__ void forward_step(const T *dx, const int (&let)[kMaxDepth], const Item &it,
-                                             T (&pref)[kMaxDepth], T (&cpref)[kMaxDepth], T (&top)[TB], T (&ctop)[TB])
+template <typename T, int K, int TB, int MK>
+__device__ __forceinline__ void forward_step(const T *dx, const int (&let)[MK], const Item &it,
+                                             T (&pref)[MK], T (&cpref)[MK], T (&top)[TB], T (&ctop)[TB])
 {
     T xs[K > 1 ? K - 1 : 1];
 #pragma unroll
@@ -159,8 +165,8 @@ __device__ __forceinline__ void forward_step(const T *dx, const int (&let)[kMaxD
 }
 
 // ---- forward step of the prefixes only (uncompensated), used to rebuild them for backward ----
-template <typename T, int K>
-__device__ __forceinline__ void prefix_step(const T *dx, const int (&let)[kMaxDepth], T (&pref)[kMaxDepth])
+template <typename T, int K, int MK>
+__device__ __forceinline__ void prefix_step(const T *dx, const int (&let)[MK], T (&pref)[MK])
 {
     T xs[K > 1 ? K - 1 : 1];
 #pragma unroll
@@ -178,9 +184,9 @@ __device__ __forceinline__ void prefix_step(const T *dx, const int (&let)[kMaxDe
 // Rolls pref back to the previous point, pushes the adjoints apref through the transposed
 // chains and adds this thread's share of dL/d(dx_t) into sg (private slot, or the block's
 // shared row with atomics).
-template <typename T, int K, int TB>
-__device__ __forceinline__ void backward_step(const T *dx, const int (&let)[kMaxDepth], const Item &it,
-                                              T (&pref)[kMaxDepth], T (&apref)[kMaxDepth], const T (&g)[TB], T *sg,
+template <typename T, int K, int TB, int MK>
+__device__ __forceinline__ void backward_step(const T *dx, const int (&let)[MK], const Item &it,
+                                              T (&pref)[MK], T (&apref)[MK], const T (&g)[TB], T *sg,
                                               bool slots)
 {
     T xs[K > 1 ? K - 1 : 1], lg[K > 1 ? K - 1 : 1];
@@ -236,20 +242,25 @@ __device__ __forceinline__ void backward_step(const T *dx, const int (&let)[kMax
     }
 }
 
-#define PSIG_SWITCH_DEGREE(k, ...)                                           \
+// Runs the statement with K = k as a compile-time constant; degrees above MK (the bound of the
+// kernel instance) are not instantiated.
+#define PSIG_DEGREE_CASE(n, MK, ...) \
+    case n: { constexpr int K = n; if constexpr (K <= (MK)) { __VA_ARGS__; } } break;
+#define PSIG_SWITCH_DEGREE(k, MK, ...)                                       \
     switch (k) {                                                             \
-        case 1: { constexpr int K = 1; __VA_ARGS__; } break;                 \
-        case 2: { constexpr int K = 2; __VA_ARGS__; } break;                 \
-        case 3: { constexpr int K = 3; __VA_ARGS__; } break;                 \
-        case 4: { constexpr int K = 4; __VA_ARGS__; } break;                 \
-        case 5: { constexpr int K = 5; __VA_ARGS__; } break;                 \
-        case 6: { constexpr int K = 6; __VA_ARGS__; } break;                 \
-        case 7: { constexpr int K = 7; __VA_ARGS__; } break;                 \
-        case 8: { constexpr int K = 8; __VA_ARGS__; } break;                 \
-        case 9: { constexpr int K = 9; __VA_ARGS__; } break;                 \
-        case 10: { constexpr int K = 10; __VA_ARGS__; } break;               \
-        case 11: { constexpr int K = 11; __VA_ARGS__; } break;               \
-        default: { constexpr int K = 12; __VA_ARGS__; } break;               \
+        PSIG_DEGREE_CASE(1, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(2, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(3, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(4, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(5, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(6, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(7, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(8, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(9, MK, __VA_ARGS__)                                 \
+        PSIG_DEGREE_CASE(10, MK, __VA_ARGS__)                                \
+        PSIG_DEGREE_CASE(11, MK, __VA_ARGS__)                                \
+        PSIG_DEGREE_CASE(12, MK, __VA_ARGS__)                                \
+        default: break;                                                      \
     }
 
 template <typename T, int TB>
@@ -259,9 +270,9 @@ __global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T *s_dx = reinterpret_cast<T *>(smem_raw);
     const int d = p.lt.d;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kBlock + threadIdx.x, p.item_start);
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kBlock + threadIdx.x, p.item_start, p.items, p.tiles);
     int let[kMaxDepth];
-    prefix_letters(it, d, let);
+    prefix_letters<kMaxDepth>(it, d, let);
     const long long units = p.B * p.W;
 
     for (long long unit = blockIdx.y; unit < units; unit += gridDim.y) {
@@ -282,8 +293,9 @@ __global__ void __launch_bounds__(kBlock) sig_forward_generic(const GenericPlan 
             __syncthreads();
             if (it.nb == 0) continue;
             // dispatch on the degree once per chunk, so the step loop itself is branch-free
-            PSIG_SWITCH_DEGREE(it.K, {
-                for (int t = 0; t < n; ++t) forward_step<T, K, TB>(s_dx + t * d, let, it, pref, cpref, top, ctop);
+            PSIG_SWITCH_DEGREE(it.K, kMaxDepth, {
+                for (int t = 0; t < n; ++t)
+                    forward_step<T, K, TB, kMaxDepth>(s_dx + t * d, let, it, pref, cpref, top, ctop);
             });
         }
         if (it.nb == 0) continue;
@@ -309,9 +321,9 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
     T *s_gd = s_dx + (size_t)p.chunk * p.lt.d;
     const int d = p.lt.d;
     const long long block_first = (long long)blockIdx.x * kBlock;
-    const Item it = decode_item<TB>(p, block_first + threadIdx.x, p.item_start);
+    const Item it = decode_item<TB>(p, block_first + threadIdx.x, p.item_start, p.items, p.tiles);
     int let[kMaxDepth];
-    prefix_letters(it, d, let);
+    prefix_letters<kMaxDepth>(it, d, let);
     const bool slots = p.slot_stride > 0;
     const int nact = (int)max(0LL, min((long long)kBlock, p.item_start[p.lt.depth + 1] - block_first));
     // does any item of this block have to rebuild its prefix values with a forward sweep?
@@ -359,8 +371,8 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
                 stage_increments(x, d, c0, n, s_dx);
                 __syncthreads();
                 if (!rebuild) continue;
-                PSIG_SWITCH_DEGREE(it.K, {
-                    for (int t = 0; t < n; ++t) prefix_step<T, K>(s_dx + t * d, let, pref);
+                PSIG_SWITCH_DEGREE(it.K, kMaxDepth, {
+                    for (int t = 0; t < n; ++t) prefix_step<T, K, kMaxDepth>(s_dx + t * d, let, pref);
                 });
             }
         }
@@ -387,9 +399,10 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
             if (it.nb > 0) {
                 const size_t t_stride = slots ? (size_t)kBlock * p.slot_stride : (size_t)d;
                 T *sg0 = slots ? s_gd + (size_t)threadIdx.x * p.slot_stride : s_gd;
-                PSIG_SWITCH_DEGREE(it.K, {
+                PSIG_SWITCH_DEGREE(it.K, kMaxDepth, {
                     for (int t = n - 1; t >= 0; --t)
-                        backward_step<T, K, TB>(s_dx + t * d, let, it, pref, apref, g, sg0 + t * t_stride, slots);
+                        backward_step<T, K, TB, kMaxDepth>(s_dx + t * d, let, it, pref, apref, g, sg0 + t * t_stride,
+                                                           slots);
                 });
             }
             __syncthreads();
@@ -423,6 +436,7 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
 #endif
 constexpr int kLaneWarps = PSIG_LANE_WARPS;
 constexpr int kLaneBlock = 32 * kLaneWarps;
+constexpr int kLaneShallow = 6;  // depths up to this run an instance with per-thread arrays of this size
 
 struct LaneUnit {  // per-unit facts, published once per unit group in shared memory
     long long b;
@@ -472,7 +486,7 @@ __device__ __forceinline__ void stage_unit_increments(const GenericPlan &p, cons
     }
 }
 
-template <typename T, int TB>
+template <typename T, int TB, int MK>
 __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPlan p, const T *__restrict__ path,
                                                                 T *__restrict__ out)
 {
@@ -480,9 +494,10 @@ __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPla
     T *s_dx = reinterpret_cast<T *>(smem_raw);
     __shared__ LaneUnit s_unit[32];
     const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start);
-    int let[kMaxDepth];
-    prefix_letters(it, d, let);
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start, p.lane_items,
+                                    p.lane_tiles);
+    int let[MK];
+    prefix_letters<MK>(it, d, let);
     const long long units = p.B * p.W, groups = (units + 31) / 32;
 
     for (long long group = blockIdx.y; group < groups; group += gridDim.y) {
@@ -493,9 +508,9 @@ __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPla
         int max_steps = 0;
         for (int r = 0; r < 32; ++r) max_steps = max(max_steps, s_unit[r].steps);
 
-        T pref[kMaxDepth], cpref[kMaxDepth], top[TB], ctop[TB];
+        T pref[MK], cpref[MK], top[TB], ctop[TB];
 #pragma unroll
-        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); cpref[j] = T(0); }
+        for (int j = 0; j < MK; ++j) { pref[j] = T(0); cpref[j] = T(0); }
 #pragma unroll
         for (int i = 0; i < TB; ++i) { top[i] = T(0); ctop[i] = T(0); }
 
@@ -507,8 +522,9 @@ __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPla
             if (it.nb == 0) continue;
             const T *mine = s_dx + lane * p.lane_stride;
             const int n_lane = min(n, steps - c0);  // steps of this lane's unit inside the chunk
-            PSIG_SWITCH_DEGREE(it.K, {
-                for (int t = 0; t < n_lane; ++t) forward_step<T, K, TB>(mine + t * d, let, it, pref, cpref, top, ctop);
+            PSIG_SWITCH_DEGREE(it.K, MK, {
+                for (int t = 0; t < n_lane; ++t)
+                    forward_step<T, K, TB, MK>(mine + t * d, let, it, pref, cpref, top, ctop);
             });
         }
         const long long unit = group * 32 + lane;
@@ -524,7 +540,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPla
     }
 }
 
-template <typename T, int TB>
+template <typename T, int TB, int MK>
 __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPlan p, const T *__restrict__ path,
                                                                  const T *__restrict__ sig,
                                                                  const T *__restrict__ grad,
@@ -535,9 +551,10 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
     T *s_gd = s_dx + 32 * (size_t)p.lane_stride;
     __shared__ LaneUnit s_unit[32];
     const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start);
-    int let[kMaxDepth];
-    prefix_letters(it, d, let);
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start, p.lane_items,
+                                    p.lane_tiles);
+    int let[MK];
+    prefix_letters<MK>(it, d, let);
     const bool rebuild = it.nb > 0 && !p.lt.lower_dense[it.K];
     const bool any_rebuild = __syncthreads_or(rebuild ? 1 : 0) != 0;
     const long long units = p.B * p.W, groups = (units + 31) / 32;
@@ -553,9 +570,9 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
         for (int r = 0; r < 32; ++r) max_steps = max(max_steps, s_unit[r].steps);
         if (max_steps == 0) continue;  // uniform over the block
 
-        T pref[kMaxDepth], apref[kMaxDepth], g[TB];
+        T pref[MK], apref[MK], g[TB];
 #pragma unroll
-        for (int j = 0; j < kMaxDepth; ++j) { pref[j] = T(0); apref[j] = T(0); }
+        for (int j = 0; j < MK; ++j) { pref[j] = T(0); apref[j] = T(0); }
 #pragma unroll
         for (int i = 0; i < TB; ++i) g[i] = T(0);
         if (live) {
@@ -571,7 +588,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
                 const T *srow = sig + unit * p.lt.total;
                 long long c = it.u;
 #pragma unroll
-                for (int j = kMaxDepth - 1; j >= 1; --j)
+                for (int j = MK - 1; j >= 1; --j)
                     if (j <= it.K - 1) { pref[j] = srow[p.lt.dense_offset[j] + c]; c /= d; }
             }
         }
@@ -584,8 +601,8 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
                 if (!rebuild || !live) continue;
                 const T *mine = s_dx + lane * p.lane_stride;
                 const int n_lane = min(n, steps - c0);
-                PSIG_SWITCH_DEGREE(it.K, {
-                    for (int t = 0; t < n_lane; ++t) prefix_step<T, K>(mine + t * d, let, pref);
+                PSIG_SWITCH_DEGREE(it.K, MK, {
+                    for (int t = 0; t < n_lane; ++t) prefix_step<T, K, MK>(mine + t * d, let, pref);
                 });
             }
         }
@@ -602,9 +619,9 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
                 const T *mine = s_dx + lane * p.lane_stride;
                 T *mine_gd = s_gd + lane * p.lane_stride;
                 const int n_lane = min(n, steps - c0);
-                PSIG_SWITCH_DEGREE(it.K, {
+                PSIG_SWITCH_DEGREE(it.K, MK, {
                     for (int t = n_lane - 1; t >= 0; --t)
-                        backward_step<T, K, TB>(mine + t * d, let, it, pref, apref, g, mine_gd + t * d, false);
+                        backward_step<T, K, TB, MK>(mine + t * d, let, it, pref, apref, g, mine_gd + t * d, false);
                 });
             }
             __syncthreads();
@@ -679,8 +696,22 @@ int make_plan(const PsigSigDesc &desc, const LevelTable &lt, int buffers, Generi
     // lane kernels: worth it when rows have few items and there are at least a warp's worth of units
     p.lane_chunk = 0;
     p.lane_stride = 0;
+    // A warp of the lane kernels runs ONE item, so a tile wider than the item's word count is issued
+    // in full and predicated off: rows with a projected degree use single-word items throughout.
+    bool any_projected = false;
+    for (int k = 1; k <= lt.depth; ++k) any_projected = any_projected || lt.words[k] != nullptr;
+    p.lane_tb = any_projected ? 1 : TB;
+    p.lane_tiles = (lt.d + p.lane_tb - 1) / p.lane_tb;
     long long lane_items = 0;
-    for (int k = 1; k <= lt.depth; ++k) { p.lane_start[k] = lane_items; lane_items += p.items[k]; }
+    d_pow = 1;
+    p.lane_items[0] = 0;
+    for (int k = 1; k <= kMaxDepth; ++k) p.lane_items[k] = 0;
+    for (int k = 1; k <= lt.depth; ++k) {
+        p.lane_items[k] = lt.words[k] ? lt.size[k] : (lt.size[k] == 0 ? 0 : d_pow * p.lane_tiles);
+        p.lane_start[k] = lane_items;
+        lane_items += p.lane_items[k];
+        if (k < lt.depth) d_pow *= lt.d;
+    }
     for (int k = lt.depth + 1; k <= kMaxDepth + 1; ++k) p.lane_start[k] = lane_items;
     {
         const long long units = p.B * p.W;
@@ -723,7 +754,11 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
         const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
         const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
         const size_t smem = sizeof(T) * 32 * (size_t)plan.lane_stride;
-        sig_forward_lanes<T, TB><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
+        if (single && shallow) sig_forward_lanes<T, 1, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        else if (single) sig_forward_lanes<T, 1, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        else if (shallow) sig_forward_lanes<T, TB, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        else sig_forward_lanes<T, TB, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
         return check_launch();
     }
     const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
@@ -750,7 +785,15 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
         const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
         const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
         const size_t smem = 2 * sizeof(T) * 32 * (size_t)plan.lane_stride;
-        sig_backward_lanes<T, TB><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
+        if (single && shallow)
+            sig_backward_lanes<T, 1, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        else if (single)
+            sig_backward_lanes<T, 1, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        else if (shallow)
+            sig_backward_lanes<T, TB, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        else
+            sig_backward_lanes<T, TB, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
     } else if (units > 0 && blocks > 0) {
         const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
