@@ -436,6 +436,7 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
 #endif
 constexpr int kLaneWarps = PSIG_LANE_WARPS;
 constexpr int kLaneBlock = 32 * kLaneWarps;
+constexpr int kSmCount = 148;
 constexpr int kLaneShallow = 6;  // depths up to this run an instance with per-thread arrays of this size
 
 struct LaneUnit {  // per-unit facts, published once per unit group in shared memory
@@ -460,7 +461,7 @@ __device__ __forceinline__ void stage_unit_increments(const GenericPlan &p, cons
                                                       const LaneUnit *s_unit, int c0, int n, T *s_dx)
 {
     const int d = p.lt.d, row = n * d, lane = threadIdx.x & 31;
-    for (int r = threadIdx.x >> 5; r < 32; r += kLaneWarps) {
+    for (int r = threadIdx.x >> 5; r < 32; r += (int)(blockDim.x >> 5)) {
         const LaneUnit lu = s_unit[r];
         const T *lo = path + (lu.b * p.L + lu.start + c0) * d;
         const int valid = max(0, min(n, lu.steps - c0)) * d;
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_forward_lanes(const GenericPla
     T *s_dx = reinterpret_cast<T *>(smem_raw);
     __shared__ LaneUnit s_unit[32];
     const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start, p.lane_items,
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * (blockDim.x >> 5) + warp, p.lane_start, p.lane_items,
                                     p.lane_tiles);
     int let[MK];
     prefix_letters<MK>(it, d, let);
@@ -551,7 +552,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
     T *s_gd = s_dx + 32 * (size_t)p.lane_stride;
     __shared__ LaneUnit s_unit[32];
     const int d = p.lt.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const Item it = decode_item<TB>(p, (long long)blockIdx.x * kLaneWarps + warp, p.lane_start, p.lane_items,
+    const Item it = decode_item<TB>(p, (long long)blockIdx.x * (blockDim.x >> 5) + warp, p.lane_start, p.lane_items,
                                     p.lane_tiles);
     int let[MK];
     prefix_letters<MK>(it, d, let);
@@ -613,7 +614,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
             const int n = min(p.lane_chunk, max_steps - c0);
             __syncthreads();
             stage_unit_increments(p, path, s_unit, c0, n, s_dx);
-            for (int i = threadIdx.x; i < 32 * p.lane_stride; i += kLaneBlock) s_gd[i] = T(0);
+            for (int i = threadIdx.x; i < 32 * p.lane_stride; i += blockDim.x) s_gd[i] = T(0);
             __syncthreads();
             if (live) {
                 const T *mine = s_dx + lane * p.lane_stride;
@@ -627,7 +628,7 @@ __global__ void __launch_bounds__(kLaneBlock) sig_backward_lanes(const GenericPl
             __syncthreads();
             // flush the 32 units' rows of this chunk, one unit per warp at a time
             const int row = n * d;
-            for (int r = warp; r < 32; r += kLaneWarps) {
+            for (int r = warp; r < 32; r += (int)(blockDim.x >> 5)) {
                 const LaneUnit lu = s_unit[r];
                 T *dst = inc_grad + (lu.b * (p.L - 1) + lu.start + c0) * d;
                 const T *src = s_gd + r * p.lane_stride;
@@ -659,6 +660,21 @@ __global__ void increments_to_points(const T *__restrict__ inc_grad, T *__restri
         const T before = (t > 0) ? g[(t - 1) * d] : T(0);
         path_grad[i] = before - after;
     }
+}
+
+// Warps per block of the lane kernels (16, 8 or 4): the choice that leaves the busiest SM the fewest
+// warps when the blocks are dealt round-robin over the SMs; larger blocks win ties because a block
+// stages the increments of its 32 units once for all its warps.
+int lane_warps_for(long long items, long long groups)
+{
+    int best = kLaneWarps;
+    long long best_cost = -1;
+    for (int lw = kLaneWarps; lw >= 4; lw /= 2) {
+        const long long blocks = (items + lw - 1) / lw * groups;
+        const long long cost = (blocks + kSmCount - 1) / kSmCount * lw;
+        if (best_cost < 0 || cost < best_cost) { best = lw; best_cost = cost; }
+    }
+    return best;
 }
 
 template <typename T> constexpr int tile_letters() { return sizeof(T) == 4 ? 8 : 4; }
@@ -751,14 +767,16 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
     if (units == 0 || blocks == 0) return PSIG_OK;
     if (plan.lane_chunk > 0) {
         const long long groups = (units + 31) / 32;
-        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
+        const int lw = lane_warps_for(plan.lane_start[kMaxDepth + 1], groups);
+        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + lw - 1) / lw;
         const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
+        const unsigned block = 32u * lw;
         const size_t smem = sizeof(T) * 32 * (size_t)plan.lane_stride;
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
-        if (single && shallow) sig_forward_lanes<T, 1, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
-        else if (single) sig_forward_lanes<T, 1, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
-        else if (shallow) sig_forward_lanes<T, TB, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
-        else sig_forward_lanes<T, TB, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, out);
+        if (single && shallow) sig_forward_lanes<T, 1, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, out);
+        else if (single) sig_forward_lanes<T, 1, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, out);
+        else if (shallow) sig_forward_lanes<T, TB, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, out);
+        else sig_forward_lanes<T, TB, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, out);
         return check_launch();
     }
     const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
@@ -782,18 +800,20 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
     if (cudaMemsetAsync(inc_grad_ws, 0, inc_bytes, stream) != cudaSuccess) return PSIG_ERR_CUDA;
     if (units > 0 && blocks > 0 && plan.lane_chunk > 0) {
         const long long groups = (units + 31) / 32;
-        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + kLaneWarps - 1) / kLaneWarps;
+        const int lw = lane_warps_for(plan.lane_start[kMaxDepth + 1], groups);
+        const long long lane_blocks = (plan.lane_start[kMaxDepth + 1] + lw - 1) / lw;
         const dim3 grid((unsigned)lane_blocks, (unsigned)(groups < 65535 ? groups : 65535));
+        const unsigned block = 32u * lw;
         const size_t smem = 2 * sizeof(T) * 32 * (size_t)plan.lane_stride;
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
         if (single && shallow)
-            sig_backward_lanes<T, 1, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+            sig_backward_lanes<T, 1, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         else if (single)
-            sig_backward_lanes<T, 1, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+            sig_backward_lanes<T, 1, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         else if (shallow)
-            sig_backward_lanes<T, TB, kLaneShallow><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+            sig_backward_lanes<T, TB, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         else
-            sig_backward_lanes<T, TB, kMaxDepth><<<grid, kLaneBlock, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+            sig_backward_lanes<T, TB, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
     } else if (units > 0 && blocks > 0) {
         const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
