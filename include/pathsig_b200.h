@@ -147,6 +147,28 @@ int psig_sig_backward_static(const PsigSigDesc *desc, const void *path, const vo
                              void *grad_path, void *stream);
 int64_t psig_sig_backward_static_limit(void);
 
+/* Chen product of truncated signatures; no counterpart in the reference, which always recomputes
+ * a signature from the increments (src/pathsig/forward/sig_kernels.cu:116-157).  Rows hold degrees
+ * 1..depth, all dense, in the layout of psig_sig_forward; the degree-0 coordinate (1) is implied:
+ *   out(w) = a(w) + b(w) + sum_{0<k<|w|} a(w[:k]) * b(w[k:])
+ * so out is the signature of path A followed by path B (translated to start where A ends). */
+typedef struct PsigChenDesc {
+    int32_t dtype;   /* PsigDtype */
+    int32_t d;       /* channels */
+    int32_t depth;   /* 1..12 */
+    int32_t reserved;
+    int64_t rows;    /* signature rows in a, b and out */
+} PsigChenDesc;
+
+/* Width of one row (sum of d^k, k = 1..depth), or a negative PsigStatus. */
+int64_t psig_chen_size(const PsigChenDesc *desc);
+/* out (rows, D) = a (x) b, row by row.  `out` must not alias a or b. */
+int psig_chen_forward(const PsigChenDesc *desc, const void *a, const void *b, void *out, void *stream);
+/* grad_a, grad_b (rows, D) = adjoint of psig_chen_forward applied to grad_out.  Needs no scratch and
+ * uses no atomics: results are bit-reproducible from run to run. */
+int psig_chen_backward(const PsigChenDesc *desc, const void *a, const void *b, const void *grad_out,
+                       void *grad_a, void *grad_b, void *stream);
+
 /* Measurement aid with no counterpart in the reference: launches `blocks` x 256 threads that each
  * run `iters` x 128 dependent-chain-free FP32 FMAs on registers only, and returns the number of
  * FMAs issued (or a negative PsigStatus).  Timed by the caller, it gives the FP32 FMA peak used

@@ -14,8 +14,24 @@ from . import ops  # noqa: E402  (registers torch.ops.pathsig_b200.*)
 from .modules import LogSignature, Signature  # noqa: E402
 from .projections import projections  # noqa: E402
 
-__all__ = ["Signature", "LogSignature", "projections", "install_as_pathsig"]
+__all__ = ["Signature", "LogSignature", "projections", "chen_product", "install_as_pathsig"]
 __version__ = "0.1.0"
+
+
+def chen_product(sig_a, sig_b, *, path_dim: int, depth: int):
+    """Signature of two paths run one after the other, from their signatures (Chen's identity).
+
+    ``sig_a`` and ``sig_b`` are dense signatures ``(..., D)`` as :class:`Signature` returns them
+    without a projection (``D = path_dim + ... + path_dim**depth``); the result has the same shape and
+    is differentiable wrt both.  ``chen_product(S(x[:, :m+1]), S(x[:, m:]))`` equals ``S(x)``.  The
+    reference package has no counterpart; signatures of adjoining or growing pieces of a path can be
+    combined with it instead of being recomputed from the points.
+    """
+    if not isinstance(path_dim, int) or path_dim < 1:
+        raise ValueError("path_dim must be a positive integer")
+    if not isinstance(depth, int) or not (1 <= depth <= 12):
+        raise ValueError("depth must be an integer in [1, 12]")
+    return ops.chen_product(sig_a, sig_b, depth, path_dim)
 
 
 def install_as_pathsig(register_ops: bool = True) -> None:

@@ -55,9 +55,20 @@ class LogDesc(ctypes.Structure):
     ]
 
 
+class ChenDesc(ctypes.Structure):
+    """``PsigChenDesc`` of include/pathsig_b200.h."""
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("d", ctypes.c_int32),
+        ("depth", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("rows", ctypes.c_int64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/pathsig_b200.h declares.
 _vp, _i64, _int = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
-_SigP, _LogP = ctypes.POINTER(SigDesc), ctypes.POINTER(LogDesc)
+_SigP, _LogP, _ChenP = ctypes.POINTER(SigDesc), ctypes.POINTER(LogDesc), ctypes.POINTER(ChenDesc)
 EXPORTS = {
     "psig_abi_version": (_int, []),
     "psig_status_string": (ctypes.c_char_p, [_int]),
@@ -73,6 +84,9 @@ EXPORTS = {
     "psig_probe_fp32_fma_packed": (_i64, [_int, _int, _vp, _vp]),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),
     "psig_sig_backward_static_limit": (_i64, []),
+    "psig_chen_size": (_i64, [_ChenP]),
+    "psig_chen_forward": (_int, [_ChenP, _vp, _vp, _vp, _vp]),
+    "psig_chen_backward": (_int, [_ChenP, _vp, _vp, _vp, _vp, _vp, _vp]),
 }
 
 

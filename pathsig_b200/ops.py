@@ -24,7 +24,7 @@ from torch import Tensor
 from . import _load
 
 __all__ = ["compute_signature", "sig_to_logsig", "signature_backward", "logsig_backward",
-           "register_namespace", "NAMESPACE"]
+           "chen_product", "chen_product_backward", "register_namespace", "NAMESPACE"]
 
 NAMESPACE = "pathsig_b200"
 
@@ -38,6 +38,9 @@ _SCHEMAS = {
                      "Tensor encoded_words, int[] level_sizes) -> (Tensor, Tensor)",
     "logsig_backward": "(Tensor signature_in, Tensor P_in, Tensor grad_logsig_in, int depth, "
                        "bool alternative_projection, Tensor encoded_words, int[] level_sizes) -> Tensor",
+    # not in the reference: Chen product of two dense truncated signatures and its adjoint
+    "chen_product": "(Tensor sig_a, Tensor sig_b, int depth, int d) -> Tensor",
+    "chen_product_backward": "(Tensor sig_a, Tensor sig_b, Tensor grad_out, int depth, int d) -> (Tensor, Tensor)",
 }
 
 # Kernel family used by the signature operators: _load.ALGO_AUTO / ALGO_GENERIC / ALGO_TILED.
@@ -275,6 +278,59 @@ def _logsig_backward_cuda(signature_in, P_in, grad_logsig_in, depth, alternative
     return grad_sig
 
 
+def _chen_desc(sig_a: Tensor, sig_b: Tensor, depth: int, d: int) -> _load.ChenDesc:
+    depth, d = int(depth), int(d)
+    if not sig_a.is_cuda or not sig_b.is_cuda:
+        raise RuntimeError("signatures must be CUDA")
+    if not (1 <= depth <= _load.MAX_DEPTH):
+        raise RuntimeError("depth must be in [1,12]")
+    if d < 1:
+        raise RuntimeError("d must be >= 1")
+    if sig_a.dtype != sig_b.dtype:
+        raise RuntimeError("signatures must have the same dtype")
+    if sig_a.shape != sig_b.shape or sig_a.dim() < 1:
+        raise RuntimeError("signatures must have the same shape (..., D)")
+    D = sum(d ** k for k in range(1, depth + 1))
+    if sig_a.size(-1) != D:
+        raise RuntimeError(f"signature width {sig_a.size(-1)} is not the dense width {D} for d={d}, depth={depth}")
+    desc = _load.ChenDesc()
+    desc.dtype = _dtype_id(sig_a)
+    desc.d, desc.depth = d, depth
+    desc.rows = sig_a.numel() // D
+    return desc
+
+
+def _chen_product_cuda(sig_a, sig_b, depth, d):
+    lib = _load.ensure_loaded()
+    desc = _chen_desc(sig_a, sig_b, depth, d)
+    a, b = sig_a.contiguous(), sig_b.contiguous()
+    out = torch.empty_like(a)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(a.device):
+        rc = lib.psig_chen_forward(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(out), _stream_ptr(a.device))
+    _load.check(rc, "chen_product")
+    return out
+
+
+def _chen_product_backward_cuda(sig_a, sig_b, grad_out, depth, d):
+    lib = _load.ensure_loaded()
+    desc = _chen_desc(sig_a, sig_b, depth, d)
+    if not grad_out.is_cuda:
+        raise RuntimeError("grad_out must be CUDA")
+    if grad_out.dtype != sig_a.dtype or grad_out.shape != sig_a.shape:
+        raise RuntimeError("grad_out must match the signatures in dtype and shape")
+    a, b, g = sig_a.contiguous(), sig_b.contiguous(), grad_out.contiguous()
+    ga, gb = torch.empty_like(a), torch.empty_like(a)
+    if ga.numel() == 0:
+        return ga, gb
+    with torch.cuda.device(a.device):
+        rc = lib.psig_chen_backward(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(g), _ptr(ga), _ptr(gb),
+                                    _stream_ptr(a.device))
+    _load.check(rc, "chen_product_backward")
+    return ga, gb
+
+
 def _no_cpu(name):
     def impl(*args, **kwargs):
         raise NotImplementedError(
@@ -367,6 +423,19 @@ def _fake_logsig_backward(signature, P_arr, grad_logsig, depth, alternative_proj
     return torch.empty_like(signature)
 
 
+def _fake_chen_product(sig_a, sig_b, depth, d):
+    torch._check(sig_a.dtype in (torch.float32, torch.float64), lambda: "signatures must be float32 or float64")
+    torch._check(sig_a.dtype == sig_b.dtype, lambda: "signatures must have the same dtype")
+    torch._check(sig_a.shape == sig_b.shape, lambda: "signatures must have the same shape")
+    torch._check(1 <= int(depth) <= 12, lambda: "depth must satisfy 1 <= depth <= 12")
+    return torch.empty_like(sig_a)
+
+
+def _fake_chen_product_backward(sig_a, sig_b, grad_out, depth, d):
+    torch._check(grad_out.shape == sig_a.shape, lambda: "grad_out must match the signatures")
+    return torch.empty_like(sig_a), torch.empty_like(sig_b)
+
+
 # --------------------------------------------------------------------------------------
 # registration
 # --------------------------------------------------------------------------------------
@@ -376,6 +445,8 @@ _IMPLS = {
     "signature_backward": (_signature_backward_cuda, _fake_signature_backward),
     "sig_to_logsig": (_sig_to_logsig_cuda, _fake_sig_to_logsig),
     "logsig_backward": (_logsig_backward_cuda, _fake_logsig_backward),
+    "chen_product": (_chen_product_cuda, _fake_chen_product),
+    "chen_product_backward": (_chen_product_backward_cuda, _fake_chen_product_backward),
 }
 _libraries = {}  # namespace -> torch.library.Library (kept alive for the life of the process)
 
@@ -420,6 +491,48 @@ def register_namespace(ns: str) -> None:
                 signature, cache, grad_logsig, ctx.depth, ctx.alt, encoded_words, ctx.level_sizes)
         return grad_sig, None, None, None, None, None
 
+    def setup_chen(ctx, inputs, output):
+        sig_a, sig_b, depth, d = inputs
+        ctx.save_for_backward(sig_a, sig_b)
+        ctx.depth, ctx.d = int(depth), int(d)
+
+    def backward_chen(ctx, grad_out):
+        sig_a, sig_b = ctx.saved_tensors
+        grad_a = grad_b = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            grad_a, grad_b = getattr(torch.ops, ns).chen_product_backward.default(sig_a, sig_b, grad_out, ctx.depth,
+                                                                                  ctx.d)
+        return (grad_a if ctx.needs_input_grad[0] else None, grad_b if ctx.needs_input_grad[1] else None, None,
+                None)
+
+    def setup_chen_bwd(ctx, inputs, output):
+        sig_a, sig_b, grad_out, depth, d = inputs
+        ctx.save_for_backward(sig_a, sig_b, grad_out)
+        ctx.depth, ctx.d = int(depth), int(d)
+
+    def backward_chen_bwd(ctx, gga, ggb):
+        # The product is bilinear, so its adjoint is linear in each of (a, grad_out) and (b, grad_out):
+        #   grad_a = adj_a(b, g), grad_b = adj_b(a, g)  with  <adj_a(b, g), x> = <g, x (x) b - b> etc.
+        # Second derivatives are composed from the same two operators.
+        sig_a, sig_b, grad_out = ctx.saved_tensors
+        op = getattr(torch.ops, ns)
+        zero = torch.zeros_like(sig_a)
+        ga = gb = gg = None
+        # d/d(grad_out): grad_a = J_a^T g, so the adjoint wrt g is J_a gga (+ J_b ggb)
+        #   J_a x = x (x) b - b  (the part of the product linear in a), J_b y = a (x) y - a
+        if ctx.needs_input_grad[2]:
+            gg = (op.chen_product.default(gga, sig_b, ctx.depth, ctx.d) - sig_b
+                  + op.chen_product.default(sig_a, ggb, ctx.depth, ctx.d) - sig_a)
+        # d/db of <gga, adj_a(b, g)> = adj_b(gga, g) - g (the bilinear part only); likewise for a
+        if ctx.needs_input_grad[1]:
+            gb = op.chen_product_backward.default(gga, zero, grad_out, ctx.depth, ctx.d)[1] - grad_out
+        if ctx.needs_input_grad[0]:
+            ga = op.chen_product_backward.default(zero, ggb, grad_out, ctx.depth, ctx.d)[0] - grad_out
+        return ga, gb, gg, None, None
+
+    torch.library.register_autograd(f"{ns}::chen_product", backward_chen, setup_context=setup_chen, lib=lib)
+    torch.library.register_autograd(f"{ns}::chen_product_backward", backward_chen_bwd,
+                                    setup_context=setup_chen_bwd, lib=lib)
     torch.library.register_autograd(f"{ns}::compute_signature", backward_sig, setup_context=setup_sig, lib=lib)
     torch.library.register_autograd(f"{ns}::sig_to_logsig", backward_log, setup_context=setup_log, lib=lib)
     _libraries[ns] = lib
@@ -448,6 +561,18 @@ def signature_backward(path: Tensor, signature: Tensor, grad_signature: Tensor, 
     """dL/dpath from dL/dsignature."""
     return _ops.signature_backward.default(path, signature, grad_signature, depth, alternative_projection,
                                            encoded_words, level_sizes, use_windows, windows)
+
+
+def chen_product(sig_a: Tensor, sig_b: Tensor, depth: int, d: int) -> Tensor:
+    """Truncated tensor product of two dense signatures ``(..., D)`` of ``d`` channels up to ``depth``:
+    the signature of the first path followed by the second (Chen's identity).  Differentiable (twice)
+    wrt both arguments.  Not an operator of the reference."""
+    return _ops.chen_product.default(sig_a, sig_b, depth, d)
+
+
+def chen_product_backward(sig_a: Tensor, sig_b: Tensor, grad_out: Tensor, depth: int, d: int) -> Tuple[Tensor, Tensor]:
+    """(dL/dsig_a, dL/dsig_b) from dL/d(chen_product)."""
+    return _ops.chen_product_backward.default(sig_a, sig_b, grad_out, depth, d)
 
 
 def logsig_backward(signature: Tensor, P_arr: Tensor, grad_logsig: Tensor, depth: int,
