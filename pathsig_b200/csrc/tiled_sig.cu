@@ -39,9 +39,10 @@ struct Shape {
     static_assert(D % DA == 0, "DA must divide D");
     static constexpr int Q = N - P;  // depth of the register sub-tree
     static_assert(Q <= 3, "sub-tree depth above 3 is not implemented");
-    static_assert(D % 2 == 0 && DA % 2 == 0, "packed FMAs pair neighbouring letters");
     static constexpr int SPLIT = D / DA;
     static constexpr int TPU = ipow(D, P) * SPLIT;  // threads per (path, window) unit
+    // Blocks of NT threads cover a unit; when NT does not divide TPU the last block has idle threads.
+    __host__ __device__ static constexpr int parts(int nt) { return (TPU + nt - 1) / nt; }
     static constexpr int n1 = DA;
     static constexpr int n2 = Q >= 2 ? DA * D : 0;
     static constexpr int n3 = Q >= 3 ? DA * D * D : 0;
@@ -290,8 +291,10 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
             for (int c = 0; c < D; ++c) {
                 const float v2 = fmaf(v1h, o.dxf1[c], s.R2[a * D + c]);
 #pragma unroll
-                for (int e = 0; e < D; e += 2)
+                for (int e = 0; e + 1 < D; e += 2)
                     fma_pair(s.R3[(a * D + c) * D + e], s.R3[(a * D + c) * D + e + 1], v2, v2, o.dxf1[e], o.dxf1[e + 1]);
+                if constexpr (D % 2 == 1)
+                    s.R3[(a * D + c) * D + D - 1] = fmaf(v2, o.dxf1[D - 1], s.R3[(a * D + c) * D + D - 1]);
             }
         }
     }
@@ -305,8 +308,9 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
         for (int a = 0; a < DA; ++a) {
             const float v1 = fmaf(bbh, o.dxa1[a], s.R1[a]);
 #pragma unroll
-            for (int c = 0; c < D; c += 2)
+            for (int c = 0; c + 1 < D; c += 2)
                 fma_pair(s.R2[a * D + c], s.R2[a * D + c + 1], v1, v1, o.dxf1[c], o.dxf1[c + 1]);
+            if constexpr (D % 2 == 1) s.R2[a * D + D - 1] = fmaf(v1, o.dxf1[D - 1], s.R2[a * D + D - 1]);
         }
     }
     {  // target degree P+1
@@ -315,7 +319,8 @@ __device__ __forceinline__ void forward_step(ForwardState<D, N, P, DA> &s, const
 #pragma unroll
         for (int j = 1; j <= P; ++j) bb = fmaf(bb, o.xs[j - 1] * recip<float>(k - j + 1), s.pref[j]);
 #pragma unroll
-        for (int a = 0; a < DA; a += 2) fma_pair(s.R1[a], s.R1[a + 1], bb, bb, o.dxa1[a], o.dxa1[a + 1]);
+        for (int a = 0; a + 1 < DA; a += 2) fma_pair(s.R1[a], s.R1[a + 1], bb, bb, o.dxa1[a], o.dxa1[a + 1]);
+        if constexpr (DA % 2 == 1) s.R1[DA - 1] = fmaf(bb, o.dxa1[DA - 1], s.R1[DA - 1]);
     }
     // the shared prefixes, highest first so each reads the previous step's lower values
 #pragma unroll
@@ -336,14 +341,21 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
                                                               const long long *__restrict__ top_words, int top_size)
 {
     using S = Shape<D, N, P, DA>;
-    constexpr int Q = S::Q, PARTS = S::TPU / NT, CH = kFwdChunk;
+    constexpr int Q = S::Q, PARTS = S::parts(NT), CH = kFwdChunk;
+    constexpr bool PADDED = S::TPU % NT != 0;  // the unit's last block has threads without work
     extern __shared__ __align__(16) float s_top[];  // D^N floats, only when the top degree is projected
-    static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
     __shared__ __align__(16) float s_dx[1][CH][D];
     __shared__ __align__(16) PointPipe<D, BULK ? CH + 1 : 1> s_pipe;  // one float per buffer when unused
 
     const long long unit = blockIdx.x / PARTS;
-    const int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
+    int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
+    bool active = true;
+    if constexpr (PADDED) {
+        // idle threads shadow the unit's last thread (they take part in staging and barriers) and
+        // store nothing
+        active = tu < S::TPU;
+        tu = min(tu, S::TPU - 1);
+    }
     const int u = tu / S::SPLIT;
     const int a0 = (tu % S::SPLIT) * DA;
     int let[P];
@@ -466,28 +478,34 @@ __global__ void __launch_bounds__(NT, MINB) sig_forward_tiled(const float *__res
     const long long width = PROJ ? S::dense_off(N) + top_size : S::TOTAL;
     float *row = out + unit * width;
     const bool vec1 = S::kVecFirst && vec_ok, vec = S::kVecDeep && vec_ok;
+    if (active) {
 #pragma unroll
-    for (int j = 1; j <= P; ++j) {
-        const int span = ipow(D, P - j) * S::SPLIT;  // threads sharing the prefix of length j
-        if (tu % span == 0) row[S::dense_off(j) + tu / span] = st.pref[j];
+        for (int j = 1; j <= P; ++j) {
+            const int span = ipow(D, P - j) * S::SPLIT;  // threads sharing the prefix of length j
+            if (tu % span == 0) row[S::dense_off(j) + tu / span] = st.pref[j];
+        }
     }
     const long long base1 = (long long)u * D + a0;
     if constexpr (!PROJ) {
-        store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
-        if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
-        if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
+        if (active) {
+            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
+            if constexpr (Q >= 2) store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
+            if constexpr (Q >= 3) store_run<S::n3>(row + S::dense_off(P + 3) + base1 * D * D, st.R3, vec);
+        }
     } else {
         // the block holds the whole unit (checked by the launcher): stage the dense top degree in
         // shared memory and copy out the requested words
-        if constexpr (Q == 1) {
-            store_run<S::n1>(s_top + base1, st.R1, true);
-        } else if constexpr (Q == 2) {
-            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
-            store_run<S::n2>(s_top + base1 * D, st.R2, true);
-        } else {
-            store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
-            store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
-            store_run<S::n3>(s_top + base1 * D * D, st.R3, true);
+        if (active) {
+            if constexpr (Q == 1) {
+                store_run<S::n1>(s_top + base1, st.R1, true);
+            } else if constexpr (Q == 2) {
+                store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
+                store_run<S::n2>(s_top + base1 * D, st.R2, true);
+            } else {
+                store_run<S::n1>(row + S::dense_off(P + 1) + base1, st.R1, vec1);
+                store_run<S::n2>(row + S::dense_off(P + 2) + base1 * D, st.R2, vec);
+                store_run<S::n3>(s_top + base1 * D * D, st.R3, true);
+            }
         }
         block_sync<NT>();
         for (int i = threadIdx.x; i < top_size; i += NT) row[S::dense_off(N) + i] = s_top[top_words[i]];
@@ -569,10 +587,16 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
         const float bb = bc[P];
         float adj0 = 0.f, adj1 = 0.f;
 #pragma unroll
-        for (int a = 0; a < DA; a += 2) {
+        for (int a = 0; a + 1 < DA; a += 2) {
             if constexpr (Q >= 2) fma_pair(s.RS1[a], s.RS1[a + 1], -bb, -bb, o.dxa1[a], o.dxa1[a + 1]);
             fma_pair(adj0, adj1, s.RG1[a], s.RG1[a + 1], o.dxa1[a], o.dxa1[a + 1]);
             fma_pair(gda[a], gda[a + 1], s.RG1[a], s.RG1[a + 1], bb, bb);
+        }
+        if constexpr (DA % 2 == 1) {
+            constexpr int a = DA - 1;
+            if constexpr (Q >= 2) s.RS1[a] = fmaf(-bb, o.dxa1[a], s.RS1[a]);
+            adj0 = fmaf(s.RG1[a], o.dxa1[a], adj0);
+            gda[a] = fmaf(s.RG1[a], bb, gda[a]);
         }
         back_chain<P, k>(adj0 + adj1, bc, o.xs, s.apref, lg);
     }
@@ -592,12 +616,19 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
             else v1 = fmaf(bbh, o.dxa1[a], s.RS1[a]);
             float av_even = 0.f, av_odd = 0.f;
 #pragma unroll
-            for (int c = 0; c < D; c += 2) {
+            for (int c = 0; c + 1 < D; c += 2) {
                 if constexpr (Q >= 3)
                     fma_pair(s.RS2[a * D + c], s.RS2[a * D + c + 1], -v1, -v1, o.dxf1[c], o.dxf1[c + 1]);
                 const float g0 = s.RG2[a * D + c], g1 = s.RG2[a * D + c + 1];
                 fma_pair(av_even, av_odd, g0, g1, o.dxf1[c], o.dxf1[c + 1]);
                 fma_pair(gdf[c], gdf[c + 1], g0, g1, v1, v1);
+            }
+            if constexpr (D % 2 == 1) {
+                constexpr int c = D - 1;
+                if constexpr (Q >= 3) s.RS2[a * D + c] = fmaf(-v1, o.dxf1[c], s.RS2[a * D + c]);
+                const float g0 = s.RG2[a * D + c];
+                av_even = fmaf(g0, o.dxf1[c], av_even);
+                gdf[c] = fmaf(g0, v1, gdf[c]);
             }
             const float av = av_even + av_odd;
             s.RG1[a] += av;
@@ -628,10 +659,16 @@ __device__ __forceinline__ void backward_step(BackwardState<D, N, P, DA> &s, con
                 const float v2 = fmaf(v1h, o.dxf1[c], s.RS2[a * D + c]);
                 float av2_even = 0.f, av2_odd = 0.f;
 #pragma unroll
-                for (int e = 0; e < D; e += 2) {
+                for (int e = 0; e + 1 < D; e += 2) {
                     const float g0 = s.RG3[(a * D + c) * D + e], g1 = s.RG3[(a * D + c) * D + e + 1];
                     fma_pair(av2_even, av2_odd, g0, g1, o.dxf1[e], o.dxf1[e + 1]);
                     fma_pair(gdf[e], gdf[e + 1], g0, g1, v2, v2);
+                }
+                if constexpr (D % 2 == 1) {
+                    constexpr int e = D - 1;
+                    const float g0 = s.RG3[(a * D + c) * D + e];
+                    av2_even = fmaf(g0, o.dxf1[e], av2_even);
+                    gdf[e] = fmaf(g0, v2, gdf[e]);
                 }
                 const float av2 = av2_even + av2_odd;
                 s.RG2[a * D + c] += av2;
@@ -705,8 +742,8 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
 {
     using S = Shape<D, N, P, DA>;
     using SM = BackwardSmem<D, N, P, DA, NT, CHR>;
-    constexpr int Q = S::Q, PARTS = S::TPU / NT;
-    static_assert(S::TPU % NT == 0, "block size must divide the threads of a unit");
+    constexpr int Q = S::Q, PARTS = S::parts(NT);
+    constexpr bool PADDED = S::TPU % NT != 0;  // the unit's last block has threads without work
     static_assert(NT % 4 == 0, "block size must be a multiple of 4");
     extern __shared__ __align__(16) float smem[];
     float (*s_dx)[CHR][D] = reinterpret_cast<float (*)[CHR][D]>(smem);
@@ -716,7 +753,13 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
     const long long unit = blockIdx.x / PARTS;
     // slice-major thread order: all prefixes of slice 0, then slice 1, ... (keeps a0 block-uniform)
     constexpr int PREFIXES = ipow(D, P);
-    const int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
+    int tu = (int)(blockIdx.x % PARTS) * NT + threadIdx.x;
+    bool active = true;
+    if constexpr (PADDED) {
+        // idle threads shadow the unit's last thread in the loads and publish zeros
+        active = tu < S::TPU;
+        tu = min(tu, S::TPU - 1);
+    }
     const int split = tu / PREFIXES;
     const int u = tu - split * PREFIXES;
     const int a0 = split * DA;
@@ -792,8 +835,17 @@ __global__ void __launch_bounds__(NT, MINB) sig_backward_tiled(const float *__re
 #pragma unroll
         for (int j = 0; j < P; ++j) xs_next[j] = s_dx[0][n - 1][let[j]];
 #endif
+        if constexpr (PADDED) {
+            if (!active) {
+                for (int t = 0; t < n; ++t) {
+                    float *slot = s_part + t * SM::kPartRow + threadIdx.x * SM::kSlot;
+#pragma unroll
+                    for (int e = 0; e < D; ++e) slot[e] = 0.f;
+                }
+            }
+        }
 #pragma unroll 1
-        for (int t = n - 1; t >= 0; --t) {
+        for (int t = active ? n - 1 : -1; t >= 0; --t) {
             StepOperands<D, DA, P, SM::kHalf> o;
 #if PSIG_PREFETCH_XS_BWD
 #pragma unroll
@@ -957,13 +1009,44 @@ using Cfg_16_4 = Config<PSIG_CFG_16_4>;
 using Cfg_16_3 = Config<PSIG_CFG_16_3>;
 using Cfg_4_6 = Config<PSIG_CFG_4_6>;
 
+// Further shapes, not tuned one by one: the prefix length leaves a sub-tree of two or three degrees
+// that fits the registers, the block is the unit's thread count rounded up to whole warps (one
+// block per unit where that is at most 256 threads, so that a projected top degree is served too).
+//                      D  N  PF DAF NTF MINBF PB DAB NTB CHR MINBB
+using Cfg_3_5 = Config<3, 5, 3, 3, 32, 1, 3, 3, 32, 8, 1>;
+using Cfg_3_6 = Config<3, 6, 3, 3, 32, 1, 3, 3, 32, 8, 1>;
+using Cfg_3_7 = Config<3, 7, 4, 3, 96, 1, 4, 3, 96, 8, 1>;
+using Cfg_4_4 = Config<4, 4, 2, 4, 32, 1, 2, 4, 32, 8, 1>;
+using Cfg_4_5 = Config<4, 5, 3, 4, 64, 1, 3, 4, 64, 8, 1>;
+using Cfg_4_7 = Config<4, 7, 4, 4, 64, 1, 4, 4, 64, 8, 1>;
+using Cfg_5_4 = Config<5, 4, 2, 5, 32, 1, 2, 5, 32, 8, 1>;
+using Cfg_5_5 = Config<5, 5, 3, 5, 128, 1, 3, 5, 128, 8, 1>;
+using Cfg_5_6 = Config<5, 6, 3, 1, 128, 1, 3, 1, 128, 8, 1>;
+using Cfg_6_4 = Config<6, 4, 2, 3, 96, 1, 2, 3, 96, 8, 1>;
+using Cfg_6_5 = Config<6, 5, 3, 6, 224, 1, 3, 6, 224, 8, 1>;
+using Cfg_8_3 = Config<8, 3, 1, 2, 32, 1, 1, 2, 32, 8, 1>;
+using Cfg_8_5 = Config<8, 5, 3, 8, 64, 1, 3, 8, 64, 8, 1>;
+using Cfg_8_6 = Config<8, 6, 4, 8, 64, 1, 4, 8, 64, 8, 1>;
+using Cfg_10_3 = Config<10, 3, 1, 2, 64, 1, 1, 2, 64, 8, 1>;
+using Cfg_10_4 = Config<10, 4, 2, 5, 224, 1, 2, 5, 224, 8, 1>;
+using Cfg_12_3 = Config<12, 3, 1, 2, 96, 1, 1, 2, 96, 8, 1>;
+using Cfg_16_2 = Config<16, 2, 1, 8, 32, 1, 1, 8, 32, 8, 1>;
+using Cfg_32_2 = Config<32, 2, 1, 8, 128, 1, 1, 8, 128, 8, 1>;
+using Cfg_32_3 = Config<32, 3, 1, 2, 128, 1, 1, 2, 128, 4, 1>;
+
 template <typename F>
 bool dispatch(int d, int depth, F &&f)
 {
-    if (d == 8 && depth == 4) { f(Cfg_8_4{}); return true; }
-    if (d == 16 && depth == 4) { f(Cfg_16_4{}); return true; }
-    if (d == 16 && depth == 3) { f(Cfg_16_3{}); return true; }
-    if (d == 4 && depth == 6) { f(Cfg_4_6{}); return true; }
+#define PSIG_TRY(DD, NN) if (d == DD && depth == NN) { f(Cfg_##DD##_##NN{}); return true; }
+    PSIG_TRY(8, 4) PSIG_TRY(16, 4) PSIG_TRY(16, 3) PSIG_TRY(4, 6)
+    PSIG_TRY(3, 5) PSIG_TRY(3, 6) PSIG_TRY(3, 7)
+    PSIG_TRY(4, 4) PSIG_TRY(4, 5) PSIG_TRY(4, 7)
+    PSIG_TRY(5, 4) PSIG_TRY(5, 5) PSIG_TRY(5, 6)
+    PSIG_TRY(6, 4) PSIG_TRY(6, 5)
+    PSIG_TRY(8, 3) PSIG_TRY(8, 5) PSIG_TRY(8, 6)
+    PSIG_TRY(10, 3) PSIG_TRY(10, 4) PSIG_TRY(12, 3)
+    PSIG_TRY(16, 2) PSIG_TRY(32, 2) PSIG_TRY(32, 3)
+#undef PSIG_TRY
     return false;
 }
 
@@ -1007,8 +1090,8 @@ bool tiled_supported(const PsigSigDesc &desc)
     bool one_block_per_unit = false;
     const bool known = dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
-        one_block_per_unit = Shape<C::D, C::N, C::PF, C::DAF>::TPU == C::NTF &&
-                             Shape<C::D, C::N, C::PB, C::DAB>::TPU == C::NTB;
+        one_block_per_unit = Shape<C::D, C::N, C::PF, C::DAF>::parts(C::NTF) == 1 &&
+                             Shape<C::D, C::N, C::PB, C::DAB>::parts(C::NTB) == 1;
     });
     if (!known) return false;
     long long top_size = 0;
@@ -1027,7 +1110,7 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
     dispatch(desc.d, desc.depth, [&](auto cfg) {
         using C = decltype(cfg);
         using S = Shape<C::D, C::N, C::PF, C::DAF>;
-        constexpr int PARTS = S::TPU / C::NTF;
+        constexpr int PARTS = S::parts(C::NTF);
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
         const long long width = projected ? S::dense_off(C::N) + top_size : S::TOTAL;
@@ -1037,17 +1120,28 @@ int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cu
         const long long *words = projected ? reinterpret_cast<const long long *>(desc.words) : nullptr;
         // Bulk (TMA) staging pays off when a unit has several chunks, so that the next chunk's copy
         // overlaps the current chunk's arithmetic; short units (one chunk) are faster with plain loads.
-        const bool bulk = kUseBulkCopies && aligned16(path) && desc.W == 0 && desc.L - 1 > kFwdChunk;
+        const bool bulk = kUseBulkCopies && C::D % 4 == 0 && aligned16(path) && desc.W == 0 && desc.L - 1 > kFwdChunk;
         auto launch = [&](auto kernel) {
             kernel<<<(unsigned)blocks, C::NTF, smem, stream>>>(path, out, desc.L, W, win, vec, words, (int)top_size);
         };
+        constexpr bool kBulkOk = C::D % 4 == 0;             // rows of whole 16-byte pieces
+        constexpr bool kProjOk = S::parts(C::NTF) == 1;     // the block holds the whole unit
         if (projected) {
-            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, true>);
-            else launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, false>);
+            if constexpr (kProjOk) {
+                if constexpr (kBulkOk) {
+                    if (bulk) { launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, true>); goto done; }
+                }
+                launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, true, false>);
+            } else {
+                return;  // tiled_supported() said no
+            }
         } else {
-            if (bulk) launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, true>);
-            else launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, false>);
+            if constexpr (kBulkOk) {
+                if (bulk) { launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, true>); goto done; }
+            }
+            launch(sig_forward_tiled<C::D, C::N, C::PF, C::DAF, C::NTF, C::MINBF, false, false>);
         }
+    done:
         rc = check_launch();
     });
     return rc;
@@ -1067,7 +1161,7 @@ int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *
         using C = decltype(cfg);
         using S = Shape<C::D, C::N, C::PB, C::DAB>;
         using SM = BackwardSmem<C::D, C::N, C::PB, C::DAB, C::NTB, C::CHR>;
-        constexpr int PARTS = S::TPU / C::NTB;
+        constexpr int PARTS = S::parts(C::NTB);
         const long long blocks = units * PARTS;
         if (blocks > 0x7fffffffLL) { rc = PSIG_ERR_TOO_LARGE; return; }
         // Several blocks add into the same points when windows overlap or a unit spans blocks.

@@ -201,7 +201,12 @@ def test_reference_build_agrees(ps, oracle):
 
 # ---- register-tiled kernels (float32, dense) ----
 
-TILED = [(8, 4), (16, 4), (16, 3), (4, 6)]
+TILED = [(8, 4), (16, 4), (16, 3), (4, 6),
+         (3, 5), (3, 6), (3, 7), (4, 4), (4, 5), (4, 7), (5, 4), (5, 5), (5, 6), (6, 4), (6, 5),
+         (8, 3), (8, 5), (8, 6), (10, 3), (10, 4), (12, 3), (16, 2), (32, 2), (32, 3)]
+# shapes whose unit is one thread block and whose top degree fits the shared-memory staging
+TILED_PROJECTED_TOP = [(4, 6), (8, 4), (16, 3), (3, 5), (3, 6), (3, 7), (4, 4), (4, 5), (5, 4), (5, 5), (6, 4),
+                       (6, 5), (8, 3), (10, 3), (12, 3), (16, 2), (32, 2)]
 
 
 @pytest.mark.parametrize("d,depth", TILED)
@@ -222,12 +227,12 @@ def test_tiled_unsupported_shape_is_an_error(ps):
     ps.ops.set_algorithm("tiled")
     try:
         with pytest.raises(RuntimeError):
-            ps.Signature(depth=5)(torch.zeros(1, 4, 3, device=DEV))
+            ps.Signature(depth=5)(torch.zeros(1, 4, 7, device=DEV))
     finally:
         ps.ops.set_algorithm("auto")
 
 
-@pytest.mark.parametrize("d,depth", [(4, 6), (8, 4), (16, 3)])
+@pytest.mark.parametrize("d,depth", TILED_PROJECTED_TOP)
 @pytest.mark.parametrize("windowed", [False, True])
 def test_tiled_projected_top_degree(ps, oracle, d, depth, windowed):
     """Dense degrees below a projected top degree (the LogSignature layout) on the tiled kernels."""
