@@ -197,6 +197,7 @@ int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc)
     LevelTable lt;
     const int rc = log_table(desc, &lt);
     if (rc != PSIG_OK) return rc;
+    if (horner_logsig_supported(*desc, lt)) return 0;  // the row-in-shared-memory kernel needs none
     return (int64_t)dtype_size(desc->dtype) * desc->rows * lt.total * desc->depth;
 }
 
@@ -209,7 +210,7 @@ int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *c
     if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
     if (!sig || !cache || !grad_logsig || !grad_sig) return PSIG_ERR_NULL;
     const int64_t need = psig_logsig_backward_workspace(desc);
-    if (!workspace || workspace_bytes < need) return PSIG_ERR_WORKSPACE;
+    if (need > 0 && (!workspace || workspace_bytes < need)) return PSIG_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (desc->dtype == PSIG_F32)
         return generic_logsig_backward<float>(*desc, lt, static_cast<const float *>(sig),

@@ -49,6 +49,15 @@ template <typename T>
 int generic_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *cache,
                             const T *grad_logsig, T *grad_sig, T *grad_cache_ws, cudaStream_t stream);
 
+// Row-in-shared-memory log-signature kernels (horner_logsig.cu); `supported` is a pure function
+// of the description, so forward and backward of one call always agree on the kernel family.
+bool horner_logsig_supported(const PsigLogDesc &desc, const LevelTable &lt);
+template <typename T>
+int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, cudaStream_t stream);
+template <typename T>
+int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *grad_logsig,
+                           T *grad_sig, cudaStream_t stream);
+
 // Register-tiled dense float32 kernels (tiled_sig.cu).  `supported` tells whether a kernel
 // exists for this description (dense, or dense below a projected top degree).
 bool tiled_supported(const PsigSigDesc &desc);

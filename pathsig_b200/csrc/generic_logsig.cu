@@ -22,29 +22,44 @@ struct LogPlan {
     long long dpow[kMaxDepth + 1];
 };
 
-template <typename T, int N>
+// Row positions of the proper prefixes and suffixes of word `code` (|w| = N):
+//   pref[i] = position of w[:i], suf[i] = position of w[N-i:]   (i = 1..N-1, both dense degrees).
+// IDX is a 32-bit type when every code and row position fits (64-bit integer division costs an
+// order of magnitude more than the arithmetic of a word); one division by d per prefix.
+template <typename IDX, int N>
+__device__ __forceinline__ void split_word(const LogPlan &p, IDX code, IDX (&pref)[N + 1], IDX (&suf)[N + 1])
+{
+    const IDX d = (IDX)p.lt.d;
+    IDX q = code;
+#pragma unroll
+    for (int i = N - 1; i >= 1; --i) {
+        q /= d;  // code / d^(N-i)
+        pref[i] = (IDX)p.lt.dense_offset[i] + q;
+        suf[N - i] = (IDX)p.lt.dense_offset[N - i] + (code - q * (IDX)p.dpow[N - i]);
+    }
+}
+
+template <typename T, typename IDX, int N>
 __device__ __forceinline__ void logsig_word_forward(const LogPlan &p, long long idx, const T *__restrict__ sig,
                                                     T *__restrict__ P, T *__restrict__ logsig)
 {
     const int depth = p.lt.depth;
-    const long long code = p.lt.words[N] ? p.lt.words[N][idx] : idx;
+    const IDX code = (IDX)(p.lt.words[N] ? p.lt.words[N][idx] : idx);
     T suf[N + 1];
-    long long pref_ind[N + 1];
+    IDX pref_ind[N + 1], suf_ind[N + 1];
+    split_word<IDX, N>(p, code, pref_ind, suf_ind);
 #pragma unroll
-    for (int i = 1; i < N; ++i) {
-        pref_ind[i] = p.lt.dense_offset[i] + code / p.dpow[N - i];
-        suf[i] = sig[p.lt.dense_offset[i] + code % p.dpow[i]];
-    }
-    pref_ind[N] = p.lt.offset[N] + idx;
+    for (int i = 1; i < N; ++i) suf[i] = sig[suf_ind[i]];
+    pref_ind[N] = (IDX)(p.lt.offset[N] + idx);
     suf[N] = sig[pref_ind[N]];
-    const long long P_off = pref_ind[N] * depth;
+    const long long P_off = (long long)pref_ind[N] * depth;
     P[P_off] = suf[N];
     T lw = suf[N];
 #pragma unroll
     for (int m = 2; m <= N; ++m) {
         T acc = T(0);
 #pragma unroll
-        for (int k = m - 1; k < N; ++k) acc = fma(P[pref_ind[k] * depth + (m - 2)], suf[N - k], acc);
+        for (int k = m - 1; k < N; ++k) acc = fma(P[(long long)pref_ind[k] * depth + (m - 2)], suf[N - k], acc);
         const T coeff = (m & 1) ? recip<T>(m) : -recip<T>(m);
         lw = fma(coeff, acc, lw);
         P[P_off + (m - 1)] = acc;
@@ -52,19 +67,15 @@ __device__ __forceinline__ void logsig_word_forward(const LogPlan &p, long long 
     logsig[pref_ind[N]] = lw;
 }
 
-template <typename T, int N>
+template <typename T, typename IDX, int N>
 __device__ __forceinline__ void logsig_word_backward(const LogPlan &p, long long idx, const T *__restrict__ sig,
                                                      const T *__restrict__ P, const T *__restrict__ glog,
                                                      T *__restrict__ gsig, T *__restrict__ gP)
 {
     const int depth = p.lt.depth;
-    const long long code = p.lt.words[N] ? p.lt.words[N][idx] : idx;
-    long long pref_ind[N + 1], suf_ind[N + 1];
-#pragma unroll
-    for (int i = 1; i < N; ++i) {
-        pref_ind[i] = p.lt.dense_offset[i] + code / p.dpow[N - i];
-        suf_ind[i] = p.lt.dense_offset[i] + code % p.dpow[i];
-    }
+    const IDX code = (IDX)(p.lt.words[N] ? p.lt.words[N][idx] : idx);
+    IDX pref_ind[N + 1], suf_ind[N + 1];
+    split_word<IDX, N>(p, code, pref_ind, suf_ind);
     const long long wg = p.lt.offset[N] + idx;
     const T g = glog[wg];
     T gPv[N];
@@ -78,7 +89,7 @@ __device__ __forceinline__ void logsig_word_backward(const LogPlan &p, long long
     for (int m = 2; m <= N; ++m) {
 #pragma unroll
         for (int k = m - 1; k < N; ++k) {
-            const long long pi = pref_ind[k], si = suf_ind[N - k];
+            const long long pi = (long long)pref_ind[k], si = (long long)suf_ind[N - k];
             atomicAdd(&gP[pi * depth + (m - 2)], gPv[m - 1] * sig[si]);
             atomicAdd(&gsig[si], gPv[m - 1] * P[pi * depth + (m - 2)]);
         }
@@ -101,7 +112,7 @@ __device__ __forceinline__ void logsig_word_backward(const LogPlan &p, long long
         default: { constexpr int N = 12; CALL; } break;               \
     }
 
-template <typename T>
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(kLogBlock) logsig_forward_rows(const LogPlan p, const T *__restrict__ sig,
                                                                  T *__restrict__ logsig, T *__restrict__ P)
 {
@@ -112,14 +123,14 @@ __global__ void __launch_bounds__(kLogBlock) logsig_forward_rows(const LogPlan p
         T *c = P + row * S * p.lt.depth;
         for (int n = 1; n <= p.lt.depth; ++n) {
             for (long long idx = threadIdx.x; idx < p.lt.size[n]; idx += kLogBlock) {
-                PSIG_SWITCH_DEGREE(n, (logsig_word_forward<T, N>(p, idx, s, c, l)));
+                PSIG_SWITCH_DEGREE(n, (logsig_word_forward<T, IDX, N>(p, idx, s, c, l)));
             }
             __syncthreads();
         }
     }
 }
 
-template <typename T>
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(kLogBlock) logsig_backward_rows(const LogPlan p, const T *__restrict__ sig,
                                                                   const T *__restrict__ P,
                                                                   const T *__restrict__ glog,
@@ -134,7 +145,7 @@ __global__ void __launch_bounds__(kLogBlock) logsig_backward_rows(const LogPlan 
         T *gc = gP + row * S * p.lt.depth;
         for (int n = p.lt.depth; n >= 1; --n) {
             for (long long idx = threadIdx.x; idx < p.lt.size[n]; idx += kLogBlock) {
-                PSIG_SWITCH_DEGREE(n, (logsig_word_backward<T, N>(p, idx, s, c, gl, gs, gc)));
+                PSIG_SWITCH_DEGREE(n, (logsig_word_backward<T, IDX, N>(p, idx, s, c, gl, gs, gc)));
             }
             __syncthreads();
         }
@@ -151,6 +162,12 @@ LogPlan make_log_plan(const PsigLogDesc &desc, const LevelTable &lt)
     return p;
 }
 
+// Word codes (< d^depth) and positions inside a row both fit 32 bits.
+bool narrow_indices(const LogPlan &p)
+{
+    return p.dpow[p.lt.depth] > 0 && p.dpow[p.lt.depth] <= 0x7fffffffLL && p.lt.total <= 0x7fffffffLL;
+}
+
 }  // namespace
 
 template <typename T>
@@ -158,9 +175,11 @@ int generic_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const 
                            cudaStream_t stream)
 {
     if (desc.rows == 0 || lt.total == 0) return PSIG_OK;
+    if (horner_logsig_supported(desc, lt)) return horner_logsig_forward<T>(desc, lt, sig, logsig, stream);
     const LogPlan p = make_log_plan(desc, lt);
     const unsigned grid = (unsigned)(desc.rows < (1 << 20) ? desc.rows : (1 << 20));
-    logsig_forward_rows<T><<<grid, kLogBlock, 0, stream>>>(p, sig, logsig, cache);
+    if (narrow_indices(p)) logsig_forward_rows<T, unsigned><<<grid, kLogBlock, 0, stream>>>(p, sig, logsig, cache);
+    else logsig_forward_rows<T, long long><<<grid, kLogBlock, 0, stream>>>(p, sig, logsig, cache);
     return check_launch();
 }
 
@@ -169,13 +188,20 @@ int generic_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const
                             const T *grad_logsig, T *grad_sig, T *grad_cache_ws, cudaStream_t stream)
 {
     if (desc.rows == 0 || lt.total == 0) return PSIG_OK;
+    if (horner_logsig_supported(desc, lt))
+        return horner_logsig_backward<T>(desc, lt, sig, grad_logsig, grad_sig, stream);
     const LogPlan p = make_log_plan(desc, lt);
     const size_t row_bytes = sizeof(T) * (size_t)lt.total;
     if (cudaMemsetAsync(grad_sig, 0, row_bytes * desc.rows, stream) != cudaSuccess) return PSIG_ERR_CUDA;
     if (cudaMemsetAsync(grad_cache_ws, 0, row_bytes * desc.rows * lt.depth, stream) != cudaSuccess)
         return PSIG_ERR_CUDA;
     const unsigned grid = (unsigned)(desc.rows < (1 << 20) ? desc.rows : (1 << 20));
-    logsig_backward_rows<T><<<grid, kLogBlock, 0, stream>>>(p, sig, cache, grad_logsig, grad_sig, grad_cache_ws);
+    if (narrow_indices(p))
+        logsig_backward_rows<T, unsigned><<<grid, kLogBlock, 0, stream>>>(p, sig, cache, grad_logsig, grad_sig,
+                                                                         grad_cache_ws);
+    else
+        logsig_backward_rows<T, long long><<<grid, kLogBlock, 0, stream>>>(p, sig, cache, grad_logsig, grad_sig,
+                                                                          grad_cache_ws);
     return check_launch();
 }
 

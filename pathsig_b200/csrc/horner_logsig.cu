@@ -1,0 +1,425 @@
+// Signature <-> log-signature with the row held in shared memory (float32 / float64).
+//
+// With x = S - 1 (degrees 1..N of the signature), the truncated logarithm is evaluated in Horner
+// form instead of through the powers P_m = x^{(x)m} that the reference stores
+// (src/pathsig/forward/sig_kernels.cu:214-240):
+//
+//   T_N = 1/N,   T_k = 1/k - x (x) T_{k+1}  (kept up to degree N-k),   log S = x (x) T_1.
+//
+// A product with x in word coordinates is (x (x) T)(w) = sum_{j=1}^{|w|} x(w[:j]) T(w[j:]), so only
+// degrees below N of x and of the T_k are ever re-read: they live in shared memory (two or three
+// copies of sum_{n<N} d^n scalars), the top degree of the row streams through once, and the
+// (rows, S*depth) array of powers is neither written nor read.  One thread block per row.
+//
+// Backward is the adjoint of the same recurrences, written as gathers (contiguous runs of the
+// incoming gradient, no atomics) except for the words of a projected top degree, which scatter
+// with shared-memory atomics.  The T_k are recomputed, not stored.
+//
+// Used when the per-row shared memory fits and word codes fit 32 bits; otherwise the global-memory
+// kernels of generic_logsig.cu run.
+#include "common.cuh"
+
+namespace psig {
+namespace {
+
+constexpr int kHornerBlock = 256;
+constexpr size_t kHornerMaxSmem = 160 * 1024;
+
+// Division of a 32-bit unsigned number by the channel count, which is fixed for a launch: the
+// multiply-and-shift form of Granlund & Montgomery ("Division by invariant integers using
+// multiplication", 1994) in its branch-free variant, exact for every 32-bit dividend.
+struct FastDiv {
+    unsigned mul, shift, one;  // one != 0: the divisor is 1
+    __host__ void set(unsigned d)
+    {
+        one = d == 1u ? 1u : 0u;
+        unsigned l = 0;
+        while ((1ull << l) < d) ++l;  // ceil(log2 d)
+        mul = (unsigned)((((1ull << l) - d) << 32) / d + 1ull);
+        shift = l > 0 ? l - 1u : 0u;
+    }
+    __device__ __forceinline__ unsigned div(unsigned n) const
+    {
+        const unsigned t = __umulhi(n, mul);
+        const unsigned q = (((n - t) >> 1) + t) >> shift;
+        return one ? n : q;
+    }
+};
+
+struct HornerPlan {
+    FastDiv by_d;
+    int d, depth;
+    long long rows, width;       // row width S = lower + top
+    unsigned lower;              // A = sum_{n<N} d^n: scalars of the dense degrees below the top
+    unsigned top;                // words kept at degree N
+    const long long *top_words;  // device codes, or nullptr when the top degree is dense
+    unsigned off[kMaxDepth + 2];   // off[n] = start of degree n in a dense row; off[N] = lower
+    unsigned dpow[kMaxDepth + 1];  // d^k (k < N; d^N only when it fits)
+    unsigned t_off[kMaxDepth + 1];  // backward: start of T_k (degrees 1..N-k) in the T area
+    unsigned t_total;
+};
+
+__device__ __forceinline__ int degree_at(const HornerPlan &p, unsigned i, int max_degree)
+{
+    int n = 1;
+    while (n < max_degree && i >= p.off[n + 1]) ++n;
+    return n;
+}
+
+// sum_{j=1}^{n-1} x(w[:j]) * t(w[j:]) for the word `code` of degree n; xs and ts are dense rows of the
+// degrees below N (ts without its degree-0 term).
+template <typename T>
+__device__ __forceinline__ T split_sum(const HornerPlan &p, const T *xs, const T *ts, int n, unsigned code)
+{
+    T acc = T(0);
+    unsigned q = code;
+    for (int len = 1; len < n; ++len) {  // len = length of the suffix
+        q = p.by_d.div(q);               // code of the prefix of length n - len
+        const unsigned suf = code - q * p.dpow[len];
+        acc = fma(xs[p.off[n - len] + q], ts[p.off[len] + suf], acc);
+    }
+    return acc;
+}
+
+// T_{N-1}, ..., T_1 in turn; T_k is built from T_{k+1} in the other buffer.  On return the result
+// T_1 (degrees 1..N-1) is in the buffer the function returns.  `keep`, when not null, receives a
+// copy of every T_k at keep + t_off[k].
+template <typename T>
+__device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T *tb, T *keep)
+{
+    const int N = p.depth;
+    T *cur = ta, *nxt = tb;  // cur holds T_{k+1}
+    for (int k = N - 1; k >= 1; --k) {
+        const T c = T(1) / T(k + 1);  // degree-0 term of T_{k+1}
+        const unsigned cnt = p.off[N - k + 1];  // words of degree <= N-k
+        for (unsigned i = threadIdx.x; i < cnt; i += kHornerBlock) {
+            const int n = degree_at(p, i, N - k);
+            const T v = -fma(xs[i], c, split_sum(p, xs, cur, n, i - p.off[n]));
+            nxt[i] = v;
+            if (keep) keep[p.t_off[k] + i] = v;
+        }
+        __syncthreads();
+        T *tmp = cur; cur = nxt; nxt = tmp;
+    }
+    return cur;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kHornerBlock) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
+                                                                      T *__restrict__ logsig)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *xs = reinterpret_cast<T *>(smem_raw);
+    T *ta = xs + p.lower;
+    T *tb = ta + p.lower;
+    const int N = p.depth;
+    for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T *s = sig + row * p.width;
+        T *l = logsig + row * p.width;
+        __syncthreads();  // the previous row's readers are done with the buffers
+        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) xs[i] = s[i];
+        __syncthreads();
+        const T *t1 = build_t<T>(p, xs, ta, tb, nullptr);
+        // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
+        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
+            const int n = degree_at(p, i, N - 1);
+            l[i] = xs[i] + split_sum(p, xs, t1, n, i - p.off[n]);
+        }
+        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+            const unsigned code = p.top_words ? (unsigned)p.top_words[i] : i;
+            l[p.lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
+        }
+    }
+}
+
+// ---- backward ------------------------------------------------------------------------------
+
+// Adjoint of  Y = X (x) Tn  restricted to words held in shared memory (degrees <= M <= N-1), where
+// G is the adjoint of Y (degrees 1..M), X = xs and Tn has an implied degree-0 term handled by the
+// caller:
+//   gx[u] += sign * sum_{p=1}^{M-|u|} sum_{|v|=p} G(u.v) * Tn(v)       for 1 <= |u| <= M-1
+//   gt[v] (+)= sign * sum_{m=1}^{M-|v|} sum_{|u|=m} X(u) * G(u.v)      for 1 <= |v| <= M-1
+// `gt_assign`: overwrite gt (a fresh adjoint buffer) instead of adding to it.
+// Words whose sums are long (low degrees) get a warp each, lanes striding the sum; the rest one
+// thread each.  Every thread of the block must call this (it contains warp shuffles).
+template <typename T>
+__device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, const T *xs, const T *tn, const T *G,
+                                                T sign, T *gx, T *gt, bool gt_assign)
+{
+    if (M < 2) return;
+    const unsigned words = p.off[M];  // words of degree <= M-1 (per side)
+    // degrees 1..mw get warps: their sums have off[M-m+1] terms
+    unsigned warp_words = 0;
+    for (int m = 1; m <= M - 1; ++m)
+        if (p.off[M - m + 1] >= 96u) warp_words = p.off[m + 1];
+    const unsigned warp_threads = 64u * warp_words;
+    const unsigned thread_words = words - warp_words;
+    const unsigned total = warp_threads + 2u * thread_words;
+    const unsigned span = (total + 31u) / 32u * 32u;
+    for (unsigned t = threadIdx.x; t < span; t += kHornerBlock) {
+        const bool team = t < warp_threads;
+        unsigned word, lane, stride;
+        int side;
+        if (team) {
+            const unsigned item = t >> 5;
+            side = item >= warp_words ? 1 : 0;
+            word = item - (side ? warp_words : 0u);
+            lane = t & 31u;
+            stride = 32u;
+        } else {
+            const unsigned item = t - warp_threads;
+            side = item >= thread_words ? 1 : 0;
+            word = warp_words + item - (side ? thread_words : 0u);
+            lane = 0u;
+            stride = 1u;
+        }
+        const bool live = team || t < total;
+        T acc = T(0);
+        if (live) {
+            const int n = degree_at(p, word, M - 1);
+            const unsigned code = word - p.off[n];
+            if (side == 0) {
+                for (int q = 1; n + q <= M; ++q) {
+                    const unsigned dq = p.dpow[q];
+                    const T *grun = G + p.off[n + q] + code * dq;
+                    const T *trun = tn + p.off[q];
+                    for (unsigned v = lane; v < dq; v += stride) acc = fma(grun[v], trun[v], acc);
+                }
+            } else {
+                const unsigned dn = p.dpow[n];
+                for (int m = 1; m + n <= M; ++m) {
+                    const unsigned dm = p.dpow[m];
+                    const T *xrun = xs + p.off[m];
+                    const T *gcol = G + p.off[m + n] + code;
+                    for (unsigned u = lane; u < dm; u += stride) acc = fma(xrun[u], gcol[u * dn], acc);
+                }
+            }
+        }
+        if (team) {
+#pragma unroll
+            for (int sft = 16; sft >= 1; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+        }
+        if (live && lane == 0u) {
+            if (side == 0) gx[word] += sign * acc;
+            else if (gt_assign) gt[word] = sign * acc;
+            else gt[word] += sign * acc;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
+                                                                       const T *__restrict__ glog,
+                                                                       T *__restrict__ gsig)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *xs = reinterpret_cast<T *>(smem_raw);  // x, degrees below N
+    T *gl = xs + p.lower;                      // incoming gradient, degrees below N
+    T *gx = gl + p.lower;                      // gradient wrt x, degrees below N
+    T *ga = gx + p.lower;                      // adjoint of T_k
+    T *gb = ga + p.lower;                      // adjoint of T_{k+1}
+    T *tk = gb + p.lower;                      // every T_k (degrees 1..N-k) at t_off[k]
+    const int N = p.depth;
+    for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T *s = sig + row * p.width;
+        const T *g = glog + row * p.width;
+        const T *gtop = g + p.lower;
+        T *out = gsig + row * p.width;
+        __syncthreads();
+        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
+            xs[i] = s[i];
+            const T gi = g[i];
+            gl[i] = gi;
+            gx[i] = gi;   // log S = x * 1 + ...: the degree-0 term of T_1 is 1
+            ga[i] = T(0);  // build_t scratch first, then the adjoint of T_1
+            gb[i] = T(0);
+        }
+        // the top degree of x enters only through that same term
+        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) out[p.lower + i] = gtop[i];
+        __syncthreads();
+        build_t<T>(p, xs, ga, gb, tk);  // ends with a barrier
+        const T *t1 = tk + p.t_off[1];
+        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) ga[i] = T(0);
+        __syncthreads();
+
+        // ---- log S = x (x) T_1: words below the top degree ----
+        adjoint_in_smem<T>(p, N - 1, xs, t1, gl, T(1), gx, ga, false);
+        __syncthreads();
+        // ---- the same product at the top degree ----
+        if (N >= 2) {
+            if (p.top_words == nullptr) {
+                // dense: gx[u] += sum_v gtop[u.v] T_1(v), a warp per u while the run is long
+                const unsigned long_words = [&] {
+                    unsigned w = 0;
+                    for (int m = 1; m <= N - 1; ++m)
+                        if (p.dpow[N - m] >= 64u) w = p.off[m + 1];
+                    return w;
+                }();
+                const unsigned span = ((32u * long_words + (p.lower - long_words)) + 31u) / 32u * 32u;
+                for (unsigned t = threadIdx.x; t < span; t += kHornerBlock) {
+                    const bool team = t < 32u * long_words;
+                    const unsigned word = team ? (t >> 5) : long_words + (t - 32u * long_words);
+                    const unsigned lane = team ? (t & 31u) : 0u, stride = team ? 32u : 1u;
+                    const bool live = word < p.lower;
+                    T acc = T(0);
+                    if (live) {
+                        const int m = degree_at(p, word, N - 1);
+                        const unsigned run = p.dpow[N - m];
+                        const T *grun = gtop + (size_t)(word - p.off[m]) * run;
+                        const T *trun = t1 + p.off[N - m];
+                        for (unsigned v = lane; v < run; v += stride) acc = fma(grun[v], trun[v], acc);
+                    }
+                    if (team) {
+#pragma unroll
+                        for (int sft = 16; sft >= 1; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+                    }
+                    if (live && lane == 0u) gx[word] += acc;
+                }
+                // gT_1[v] += sum_u x(u) gtop[u.v]: neighbouring threads take neighbouring v (coalesced
+                // reads of the top degree); long sums over u are cut into pieces of at most 64 terms
+                unsigned items_before = 0;
+                for (int q = 1; q <= N - 1; ++q) {
+                    const unsigned dq = p.dpow[q], du = p.dpow[N - q];
+                    const unsigned pieces = (du + 63u) / 64u;
+                    const unsigned items = dq * pieces;
+                    // this degree's items are dealt to the threads after those of the degrees before it
+                    for (unsigned it = (threadIdx.x + kHornerBlock - items_before % kHornerBlock) % kHornerBlock;
+                         it < items; it += kHornerBlock) {
+                        const unsigned piece = it / dq, v = it - piece * dq;
+                        const unsigned u0 = piece * 64u, u1 = min(du, u0 + 64u);
+                        const T *xrun = xs + p.off[N - q];
+                        T acc = T(0);
+                        for (unsigned u = u0; u < u1; ++u) acc = fma(xrun[u], gtop[(size_t)u * dq + v], acc);
+                        atomicAdd(&ga[p.off[q] + v], acc);
+                    }
+                    items_before += items;
+                }
+            } else {
+                // projected: each listed word scatters its N-1 splits
+                for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+                    const unsigned code = (unsigned)p.top_words[i];
+                    const T gw = gtop[i];
+                    unsigned q = code;
+                    for (int len = 1; len < N; ++len) {
+                        q = p.by_d.div(q);
+                        const unsigned suf = code - q * p.dpow[len];
+                        atomicAdd(&gx[p.off[N - len] + q], gw * t1[p.off[len] + suf]);
+                        atomicAdd(&ga[p.off[len] + suf], xs[p.off[N - len] + q] * gw);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- T_k = 1/k - x (x) T_{k+1},  k = 1 .. N-1;  ga = adjoint of T_k (degrees 1..N-k) ----
+        T *gk = ga, *gn = gb;
+        for (int k = 1; k <= N - 1; ++k) {
+            const int M = N - k;
+            const T c = T(1) / T(k + 1);
+            for (unsigned i = threadIdx.x; i < p.off[M + 1]; i += kHornerBlock) gx[i] -= c * gk[i];
+            for (unsigned i = threadIdx.x; i < p.off[M]; i += kHornerBlock) gn[i] = T(0);
+            __syncthreads();
+            if (k < N - 1) adjoint_in_smem<T>(p, M, xs, tk + p.t_off[k + 1], gk, T(-1), gx, gn, true);
+            __syncthreads();
+            T *tmp = gk; gk = gn; gn = tmp;
+        }
+        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) out[i] = gx[i];
+    }
+}
+
+int make_horner_plan(const PsigLogDesc &desc, const LevelTable &lt, HornerPlan *plan)
+{
+    HornerPlan &p = *plan;
+    p.d = lt.d;
+    p.by_d.set((unsigned)lt.d);
+    p.depth = lt.depth;
+    p.rows = desc.rows;
+    p.width = lt.total;
+    unsigned long long pw = 1, off = 0;
+    p.dpow[0] = 1;
+    p.off[0] = 0;
+    for (int n = 1; n <= kMaxDepth; ++n) {
+        p.off[n] = (unsigned)off;
+        if (n < lt.depth) {
+            pw *= (unsigned long long)lt.d;
+            if (pw > 0x7fffffffULL) return PSIG_ERR_UNSUPPORTED;
+            p.dpow[n] = (unsigned)pw;
+            off += pw;
+            if (off > 0x7fffffffULL) return PSIG_ERR_UNSUPPORTED;
+        } else {
+            p.dpow[n] = 0;
+        }
+    }
+    p.off[kMaxDepth + 1] = (unsigned)off;
+    p.lower = (unsigned)off;
+    // the codes of the top degree must fit 32 bits too
+    if (pw * (unsigned long long)lt.d > 0x7fffffffULL) return PSIG_ERR_UNSUPPORTED;
+    if (lt.size[lt.depth] > 0x7fffffffLL) return PSIG_ERR_UNSUPPORTED;
+    p.top = (unsigned)lt.size[lt.depth];
+    p.top_words = lt.words[lt.depth];
+    if ((long long)p.lower + (long long)p.top != lt.total) return PSIG_ERR_UNSUPPORTED;  // lower degrees must be dense
+    unsigned t = 0;
+    for (int k = 1; k <= kMaxDepth; ++k) {
+        p.t_off[k] = t;
+        if (k <= lt.depth - 1) t += p.off[lt.depth - k + 1];
+    }
+    p.t_total = t;
+    return PSIG_OK;
+}
+
+template <typename T> size_t forward_smem(const HornerPlan &p) { return sizeof(T) * 3 * (size_t)p.lower; }
+template <typename T> size_t backward_smem(const HornerPlan &p) { return sizeof(T) * (5 * (size_t)p.lower + p.t_total); }
+
+unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : (1 << 20)); }
+
+}  // namespace
+
+bool horner_logsig_supported(const PsigLogDesc &desc, const LevelTable &lt)
+{
+    HornerPlan p;
+    if (make_horner_plan(desc, lt, &p) != PSIG_OK) return false;
+    const size_t scalar = desc.dtype == PSIG_F32 ? 4 : 8;
+    return scalar * (5 * (size_t)p.lower + p.t_total) <= kHornerMaxSmem;  // backward needs the most
+}
+
+template <typename T>
+int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, cudaStream_t stream)
+{
+    HornerPlan p;
+    const int rc = make_horner_plan(desc, lt, &p);
+    if (rc != PSIG_OK) return rc;
+    const size_t smem = forward_smem<T>(p);
+    auto kernel = logsig_forward_horner<T>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return PSIG_ERR_CUDA;
+    kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
+    return check_launch();
+}
+
+template <typename T>
+int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *grad_logsig,
+                           T *grad_sig, cudaStream_t stream)
+{
+    HornerPlan p;
+    const int rc = make_horner_plan(desc, lt, &p);
+    if (rc != PSIG_OK) return rc;
+    const size_t smem = backward_smem<T>(p);
+    auto kernel = logsig_backward_horner<T>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return PSIG_ERR_CUDA;
+    kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
+    return check_launch();
+}
+
+template int horner_logsig_backward<float>(const PsigLogDesc &, const LevelTable &, const float *, const float *,
+                                           float *, cudaStream_t);
+template int horner_logsig_backward<double>(const PsigLogDesc &, const LevelTable &, const double *, const double *,
+                                            double *, cudaStream_t);
+template int horner_logsig_forward<float>(const PsigLogDesc &, const LevelTable &, const float *, float *,
+                                          cudaStream_t);
+template int horner_logsig_forward<double>(const PsigLogDesc &, const LevelTable &, const double *, double *,
+                                           cudaStream_t);
+
+}  // namespace psig
