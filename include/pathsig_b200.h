@@ -87,7 +87,8 @@ typedef struct PsigLogDesc {
     int32_t dtype;
     int32_t d;
     int32_t depth;
-    int32_t reserved;
+    int32_t algo;               /* PsigAlgo: AUTO = row-in-shared-memory kernels when the row fits,
+                                   GENERIC = always the global-memory kernels (TILED is treated as AUTO) */
     int64_t rows;               /* B or B*W */
     int64_t top_size;           /* words kept at degree `depth` */
     const int64_t *top_words;   /* device codes of the top degree, or NULL when it is dense */
@@ -116,12 +117,19 @@ int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
 int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
                       void *grad_path, void *workspace, int64_t workspace_bytes, void *stream);
 
+/* Scalars per row of the cache that psig_logsig_forward fills for psig_logsig_backward: S*depth (the
+ * powers P_m of the reference) for the global-memory kernels, 0 for the row-in-shared-memory kernels,
+ * which recompute what they need.  Host-only; depends on the description alone. */
+int64_t psig_logsig_cache_size(const PsigLogDesc *desc);
+
 /* logsig (rows, S) = word coordinates of the truncated tensor logarithm of `sig` (rows, S);
- * cache (rows, S*depth) receives the intermediate powers that psig_logsig_backward reads.
+ * cache (rows, psig_logsig_cache_size(desc)) receives what psig_logsig_backward reads back (may be
+ * NULL when that size is 0).  Forward and backward of one call must use the same desc.algo.
  * Replaces pathsig::sig_to_logsig (src/pathsig/forward/sig_launch.cu:230-339). */
 int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, void *cache, void *stream);
 
-/* Scratch bytes psig_logsig_backward needs (rows * S * depth scalars). */
+/* Scratch bytes psig_logsig_backward needs: rows * S * depth scalars for the global-memory
+ * kernels, 0 for the row-in-shared-memory kernels. */
 int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
 
 /* grad_sig (rows, S) = adjoint of psig_logsig_forward applied to grad_logsig.

@@ -48,7 +48,7 @@ class LogDesc(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("d", ctypes.c_int32),
         ("depth", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("algo", ctypes.c_int32),
         ("rows", ctypes.c_int64),
         ("top_size", ctypes.c_int64),
         ("top_words", ctypes.c_void_p),
@@ -77,6 +77,7 @@ EXPORTS = {
     "psig_sig_forward": (_int, [_SigP, _vp, _vp, _vp]),
     "psig_sig_backward_workspace": (_i64, [_SigP]),
     "psig_sig_backward": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "psig_logsig_cache_size": (_i64, [_LogP]),
     "psig_logsig_forward": (_int, [_LogP, _vp, _vp, _vp, _vp]),
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),

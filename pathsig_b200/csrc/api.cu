@@ -183,13 +183,21 @@ int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, 
     const int rc = log_table(desc, &lt);
     if (rc != PSIG_OK) return rc;
     if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
-    if (!sig || !logsig || !cache) return PSIG_ERR_NULL;
+    if (!sig || !logsig || (!cache && psig_logsig_cache_size(desc) > 0)) return PSIG_ERR_NULL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (desc->dtype == PSIG_F32)
         return generic_logsig_forward<float>(*desc, lt, static_cast<const float *>(sig), static_cast<float *>(logsig),
                                              static_cast<float *>(cache), st);
     return generic_logsig_forward<double>(*desc, lt, static_cast<const double *>(sig), static_cast<double *>(logsig),
                                           static_cast<double *>(cache), st);
+}
+
+int64_t psig_logsig_cache_size(const PsigLogDesc *desc)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    return horner_logsig_supported(*desc, lt) ? 0 : lt.total * desc->depth;
 }
 
 int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc)
@@ -208,7 +216,7 @@ int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *c
     const int rc = log_table(desc, &lt);
     if (rc != PSIG_OK) return rc;
     if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
-    if (!sig || !cache || !grad_logsig || !grad_sig) return PSIG_ERR_NULL;
+    if (!sig || !grad_logsig || !grad_sig || (!cache && psig_logsig_cache_size(desc) > 0)) return PSIG_ERR_NULL;
     const int64_t need = psig_logsig_backward_workspace(desc);
     if (need > 0 && (!workspace || workspace_bytes < need)) return PSIG_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

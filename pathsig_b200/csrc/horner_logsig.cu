@@ -23,6 +23,9 @@ namespace psig {
 namespace {
 
 constexpr int kHornerBlock = 256;
+#ifndef PSIG_HORNER_MINB
+#define PSIG_HORNER_MINB 1
+#endif
 constexpr size_t kHornerMaxSmem = 160 * 1024;
 
 // Division of a 32-bit unsigned number by the channel count, which is fixed for a launch: the
@@ -81,6 +84,57 @@ __device__ __forceinline__ T split_sum(const HornerPlan &p, const T *xs, const T
     return acc;
 }
 
+// The same sums for all d children u.a of one parent word u (degree NDEG-1 >= 1) at once: the
+// prefixes of the children are the prefixes of u, and their suffixes differ only in the last letter,
+// so the x factors and the positions are worked out once per parent and the loop over a is N-1
+// shared-memory loads and multiply-adds per word.  emit(a, sum) receives each child's sum.
+template <typename T, int NDEG, class F>
+__device__ __forceinline__ void children_sums(const HornerPlan &p, const T *xs, const T *ts, unsigned u, F &&emit)
+{
+    T xp[NDEG - 1];
+    unsigned sb[NDEG - 1];
+    unsigned q = u;
+#pragma unroll
+    for (int lp = 0; lp <= NDEG - 2; ++lp) {  // lp letters of u go to the suffix
+        const unsigned rem = u - q * p.dpow[lp];  // q = u / d^lp, rem = u % d^lp
+        xp[lp] = xs[p.off[NDEG - 1 - lp] + q];
+        sb[lp] = p.off[lp + 1] + rem * (unsigned)p.d;
+        q = p.by_d.div(q);
+    }
+    for (unsigned a = 0; a < (unsigned)p.d; ++a) {
+        T acc = T(0);
+#pragma unroll
+        for (int lp = 0; lp <= NDEG - 2; ++lp) acc = fma(xp[lp], ts[sb[lp] + a], acc);
+        emit(a, acc);
+    }
+}
+
+#define PSIG_CHILD_CASE(n, ...) \
+    case n: children_sums<T, n>(__VA_ARGS__); break;
+// Dispatch on the children's degree (2..12).
+#define PSIG_CHILDREN(n, ...)                                                                             \
+    switch (n) {                                                                                          \
+        PSIG_CHILD_CASE(2, __VA_ARGS__) PSIG_CHILD_CASE(3, __VA_ARGS__) PSIG_CHILD_CASE(4, __VA_ARGS__)   \
+        PSIG_CHILD_CASE(5, __VA_ARGS__) PSIG_CHILD_CASE(6, __VA_ARGS__) PSIG_CHILD_CASE(7, __VA_ARGS__)   \
+        PSIG_CHILD_CASE(8, __VA_ARGS__) PSIG_CHILD_CASE(9, __VA_ARGS__) PSIG_CHILD_CASE(10, __VA_ARGS__)  \
+        PSIG_CHILD_CASE(11, __VA_ARGS__) PSIG_CHILD_CASE(12, __VA_ARGS__)                                 \
+        default: break;                                                                                   \
+    }
+
+// emit(position, sum) for every word of degree 2..M (position = its place in a dense row), the block's
+// threads taking parents in turn.  M <= N-1 here (words held in shared memory).
+template <typename T, class F>
+__device__ __forceinline__ void for_words_below_top(const HornerPlan &p, int M, const T *xs, const T *ts, F &&emit)
+{
+    if (M < 2) return;
+    for (unsigned i = threadIdx.x; i < p.off[M]; i += kHornerBlock) {  // parents: degrees 1..M-1
+        const int m = degree_at(p, i, M - 1);
+        const unsigned u = i - p.off[m];
+        const unsigned first = p.off[m + 1] + u * (unsigned)p.d;
+        PSIG_CHILDREN(m + 1, p, xs, ts, u, [&](unsigned a, T acc) { emit(first + a, acc); })
+    }
+}
+
 // T_{N-1}, ..., T_1 in turn; T_k is built from T_{k+1} in the other buffer.  On return the result
 // T_1 (degrees 1..N-1) is in the buffer the function returns.  `keep`, when not null, receives a
 // copy of every T_k at keep + t_off[k].
@@ -91,13 +145,17 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
     T *cur = ta, *nxt = tb;  // cur holds T_{k+1}
     for (int k = N - 1; k >= 1; --k) {
         const T c = T(1) / T(k + 1);  // degree-0 term of T_{k+1}
-        const unsigned cnt = p.off[N - k + 1];  // words of degree <= N-k
-        for (unsigned i = threadIdx.x; i < cnt; i += kHornerBlock) {
-            const int n = degree_at(p, i, N - k);
-            const T v = -fma(xs[i], c, split_sum(p, xs, cur, n, i - p.off[n]));
+        T *kept = keep ? keep + p.t_off[k] : nullptr;
+        for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) {  // degree 1: no split
+            const T v = -xs[i] * c;
             nxt[i] = v;
-            if (keep) keep[p.t_off[k] + i] = v;
+            if (kept) kept[i] = v;
         }
+        for_words_below_top<T>(p, N - k, xs, cur, [&](unsigned pos, T acc) {
+            const T v = -fma(xs[pos], c, acc);
+            nxt[pos] = v;
+            if (kept) kept[pos] = v;
+        });
         __syncthreads();
         T *tmp = cur; cur = nxt; nxt = tmp;
     }
@@ -105,7 +163,7 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kHornerBlock) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                       T *__restrict__ logsig)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -121,13 +179,22 @@ __global__ void __launch_bounds__(kHornerBlock) logsig_forward_horner(const Horn
         __syncthreads();
         const T *t1 = build_t<T>(p, xs, ta, tb, nullptr);
         // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
-        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
-            const int n = degree_at(p, i, N - 1);
-            l[i] = xs[i] + split_sum(p, xs, t1, n, i - p.off[n]);
-        }
-        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
-            const unsigned code = p.top_words ? (unsigned)p.top_words[i] : i;
-            l[p.lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
+        if (N >= 2)
+            for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) l[i] = xs[i];
+        for_words_below_top<T>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
+        if (p.top_words == nullptr && N >= 2) {
+            // dense top degree: a thread takes a parent of degree N-1 and its d children
+            const unsigned parents = p.dpow[N - 1];
+            for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
+                const T *srun = s + p.lower + (size_t)u * p.d;
+                T *lrun = l + p.lower + (size_t)u * p.d;
+                PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
+            }
+        } else {
+            for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+                const unsigned code = p.top_words ? (unsigned)p.top_words[i] : i;
+                l[p.lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
+            }
         }
     }
 }
@@ -208,7 +275,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig)
 {
@@ -376,6 +443,7 @@ unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : 
 
 bool horner_logsig_supported(const PsigLogDesc &desc, const LevelTable &lt)
 {
+    if (desc.algo == PSIG_ALGO_GENERIC) return false;
     HornerPlan p;
     if (make_horner_plan(desc, lt, &p) != PSIG_OK) return false;
     const size_t scalar = desc.dtype == PSIG_F32 ? 4 : 8;

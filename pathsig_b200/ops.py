@@ -133,7 +133,8 @@ def _sig_desc(path: Tensor, depth: int, alt: bool, encoded_words: Tensor, level_
 
 
 def _log_desc(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: Tensor,
-              level_sizes: Sequence[int]) -> _load.LogDesc:
+              level_sizes: Sequence[int], fake: bool = False) -> _load.LogDesc:
+    """``PsigLogDesc`` for these arguments; with ``fake`` no device pointer is read (shape queries only)."""
     depth, d = int(depth), int(d)
     if not (1 <= depth <= _load.MAX_DEPTH):
         raise RuntimeError("depth must be in [1,12]")
@@ -144,17 +145,22 @@ def _log_desc(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: T
     desc = _load.LogDesc()
     desc.dtype = _dtype_id(signature)
     desc.d, desc.depth = d, depth
-    desc.rows = signature.numel() // signature.size(-1) if signature.size(-1) > 0 else 0
+    desc.algo = _algo
+    desc.rows = 0 if fake else (signature.numel() // signature.size(-1) if signature.size(-1) > 0 else 0)
     desc.top_size = d ** depth
     if alt:
-        _check_words_cuda(encoded_words)
+        if not fake:
+            _check_words_cuda(encoded_words)
         if len(level_sizes) < depth + 1:
             raise RuntimeError("level_sizes must have entries up to depth")
         desc.top_size = int(level_sizes[depth])
         if desc.top_size != d ** depth:
             if encoded_words.numel() < desc.top_size:
                 raise RuntimeError("encoded_words holds fewer codes than level_sizes[depth]")
-            desc.top_words = encoded_words.data_ptr() if encoded_words.numel() > 0 else None
+            if fake:
+                desc.top_words = 1 if encoded_words.numel() > 0 else None  # non-null marker, never read
+            else:
+                desc.top_words = encoded_words.data_ptr() if encoded_words.numel() > 0 else None
     return desc
 
 
@@ -234,7 +240,9 @@ def _sig_to_logsig_cuda(signature_in, depth, d, alternative_projection, encoded_
         if S != sig.size(-1):
             raise RuntimeError(f"signature width {sig.size(-1)} does not match the layout width {S}")
         logsig = torch.empty_like(sig)
-        cache = torch.empty(sig.shape[:-1] + (sig.size(-1) * int(depth),), dtype=sig.dtype, device=sig.device)
+        per_row = lib.psig_logsig_cache_size(ctypes.byref(desc))
+        _load.check(per_row, "sig_to_logsig")
+        cache = torch.empty(sig.shape[:-1] + (int(per_row),), dtype=sig.dtype, device=sig.device)
         rc = lib.psig_logsig_forward(ctypes.byref(desc), _ptr(sig), _ptr(logsig), _ptr(cache),
                                      _stream_ptr(sig.device))
     _load.check(rc, "sig_to_logsig")
@@ -264,9 +272,14 @@ def _logsig_backward_cuda(signature_in, P_in, grad_logsig_in, depth, alternative
     sig = signature_in.contiguous()
     cache = P_in.contiguous()
     grad = grad_logsig_in.contiguous()
-    if tuple(cache.shape) != tuple(sig.shape[:-1]) + (sig.size(-1) * int(depth),):
-        raise RuntimeError("P must be [B,(W),S*depth]")
     desc = _log_desc(sig, depth, d, alternative_projection, encoded_words, level_sizes)
+    # The cache tells which kernel family produced it: the table of powers (S*depth per row) belongs to
+    # the global-memory kernels, an empty one to the row-in-shared-memory kernels.
+    if tuple(cache.shape[:-1]) != tuple(sig.shape[:-1]) or cache.size(-1) not in (0, sig.size(-1) * int(depth)):
+        raise RuntimeError("P must be [B,(W),S*depth] (or [B,(W),0] as returned by sig_to_logsig)")
+    desc.algo = _load.ALGO_GENERIC if cache.size(-1) > 0 else _load.ALGO_AUTO
+    if lib.psig_logsig_cache_size(ctypes.byref(desc)) != cache.size(-1):
+        raise RuntimeError("P does not belong to a sig_to_logsig call with these arguments")
     grad_sig = torch.empty_like(sig)
     with torch.cuda.device(sig.device):
         ws_bytes = lib.psig_logsig_backward_workspace(ctypes.byref(desc))
@@ -404,7 +417,10 @@ def _fake_sig_to_logsig(signature, depth, d, alternative_projection, encoded_wor
     torch._check(signature.dim() in (2, 3), lambda: "signature must be 2D or 3D")
     if alternative_projection:
         _fake_check_projection(encoded_words, level_sizes, depth)
-    cache = signature.new_empty(tuple(signature.shape[:-1]) + (signature.shape[-1] * depth,))
+    desc = _log_desc(signature, depth, d, alternative_projection, encoded_words, level_sizes, fake=True)
+    per_row = _load.ensure_loaded().psig_logsig_cache_size(ctypes.byref(desc))
+    _load.check(per_row, "sig_to_logsig")
+    cache = signature.new_empty(tuple(signature.shape[:-1]) + (int(per_row),))
     return torch.empty_like(signature), cache
 
 
@@ -417,7 +433,7 @@ def _fake_logsig_backward(signature, P_arr, grad_logsig, depth, alternative_proj
     torch._check(grad_logsig.shape == signature.shape, lambda: "grad_logsig must match signature shape")
     torch._check(signature.dim() in (2, 3) and P_arr.dim() == signature.dim(), lambda: "P must match signature rank")
     torch._check(tuple(P_arr.shape[:-1]) == tuple(signature.shape[:-1])
-                 and P_arr.shape[-1] == signature.shape[-1] * depth, lambda: "P must be [B,(W),S*depth]")
+                 and P_arr.shape[-1] in (0, signature.shape[-1] * depth), lambda: "P must be [B,(W),S*depth]")
     if alternative_projection:
         _fake_check_projection(encoded_words, level_sizes, depth)
     return torch.empty_like(signature)

@@ -115,15 +115,20 @@ def _oracle_logsig(oracle, mod, x64, g64, windows):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("d,depth,projected", [(2, 5, False), (3, 4, False), (3, 5, True), (4, 6, True), (5, 2, True)])
 @pytest.mark.parametrize("windowed", [False, True])
-def test_logsignature(ps, oracle, dtype, d, depth, projected, windowed):
+@pytest.mark.parametrize("algo", ["auto", "generic"])  # row-in-shared-memory kernels / table-of-powers kernels
+def test_logsignature(ps, oracle, dtype, d, depth, projected, windowed, algo):
     x = util.brownian_path(3, 21, d, seed=17 + d, dtype=dtype)
     win = util.sliding_windows(21, 9, 4) if windowed else None
     proj = ps.projections.lyndon(depth, d) if projected else None
     mod = ps.LogSignature(depth=depth, projection=proj, windows=None if win is None else win.to(DEV))
     xg = x.to(DEV).requires_grad_(True)
-    out = mod(xg)
-    g = util.normal_like(out.shape, 23, dtype)
-    (out * g.to(DEV)).sum().backward()
+    ps.ops.set_algorithm(algo)
+    try:
+        out = mod(xg)
+        g = util.normal_like(out.shape, 23, dtype)
+        (out * g.to(DEV)).sum().backward()
+    finally:
+        ps.ops.set_algorithm("auto")
     want, want_grad = _oracle_logsig(oracle, mod, x.double(), g.double(), win)
     assert out.shape == want.shape
     assert util.rel_error(out, want) < util.TOL[dtype]

@@ -164,7 +164,12 @@ def test_fake_operators_give_reference_shapes():
     words = torch.empty(200, dtype=torch.int64, device="meta")
     assert ps.ops.compute_signature(x, 3, True, words, [0, 8, 100, 100], False, nowin).shape == (32, 208)
     logsig, cache = ps.ops.sig_to_logsig(sig, 4, 8, False, ew, [0, 8, 64, 512, 4096])
-    assert logsig.shape == (32, 4680) and cache.shape == (32, 4 * 4680)
+    # the cache is empty when the row-in-shared-memory kernels serve the shape, the reference's table of
+    # powers (S * depth per row) otherwise
+    assert logsig.shape == (32, 4680) and cache.shape == (32, 0)
+    big = torch.empty(2, 16 + 16 ** 2 + 16 ** 3 + 16 ** 4 + 16 ** 5, device="meta")
+    _, big_cache = ps.ops.sig_to_logsig(big, 5, 16, False, ew, [0] + [16 ** k for k in range(1, 6)])
+    assert big_cache.shape == (2, 5 * big.shape[1])
     assert ps.ops.signature_backward(x, sig, sig, 4, False, ew, [], False, nowin).shape == x.shape
     assert ps.ops.logsig_backward(sig, cache, sig, 4, False, ew, [0, 8, 64, 512, 4096]).shape == sig.shape
     with pytest.raises(RuntimeError):
