@@ -22,9 +22,15 @@
 namespace psig {
 namespace {
 
-constexpr int kHornerBlock = 256;
-#ifndef PSIG_HORNER_MINB
-#define PSIG_HORNER_MINB 1
+#ifndef PSIG_HORNER_BLOCK
+#define PSIG_HORNER_BLOCK 256
+#endif
+constexpr int kHornerBlock = PSIG_HORNER_BLOCK;
+#ifndef PSIG_HORNER_MINB_FWD
+#define PSIG_HORNER_MINB_FWD 1
+#endif
+#ifndef PSIG_HORNER_MINB_BWD
+#define PSIG_HORNER_MINB_BWD 1
 #endif
 constexpr size_t kHornerMaxSmem = 160 * 1024;
 
@@ -60,7 +66,11 @@ struct HornerPlan {
     unsigned dpow[kMaxDepth + 1];  // d^k (k < N; d^N only when it fits)
     unsigned t_off[kMaxDepth + 1];  // backward: start of T_k (degrees 1..N-k) in the T area
     unsigned t_total;
+    unsigned stage_top;  // backward: copy the dense top degree of the incoming gradient to shared memory
 };
+
+// Four scalars moved as one access (16 bytes of float, 32 of double).
+template <typename T> struct __align__(4 * sizeof(T)) Quad { T v[4]; };
 
 __device__ __forceinline__ int degree_at(const HornerPlan &p, unsigned i, int max_degree)
 {
@@ -108,6 +118,42 @@ __device__ __forceinline__ void children_sums(const HornerPlan &p, const T *xs, 
         emit(a, acc);
     }
 }
+
+// The same, four children at a time (d a multiple of 4): emit4(a, sums[4]) for a = 0, 4, 8, ...
+template <typename T, int NDEG, class F>
+__device__ __forceinline__ void children_sums4(const HornerPlan &p, const T *xs, const T *ts, unsigned u, F &&emit4)
+{
+    T xp[NDEG - 1];
+    unsigned sb[NDEG - 1];
+    unsigned q = u;
+#pragma unroll
+    for (int lp = 0; lp <= NDEG - 2; ++lp) {
+        const unsigned rem = u - q * p.dpow[lp];
+        xp[lp] = xs[p.off[NDEG - 1 - lp] + q];
+        sb[lp] = p.off[lp + 1] + rem * (unsigned)p.d;
+        q = p.by_d.div(q);
+    }
+    for (unsigned a = 0; a < (unsigned)p.d; a += 4) {
+        T acc[4] = {T(0), T(0), T(0), T(0)};
+#pragma unroll
+        for (int lp = 0; lp <= NDEG - 2; ++lp) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = fma(xp[lp], ts[sb[lp] + a + i], acc[i]);
+        }
+        emit4(a, acc);
+    }
+}
+
+#define PSIG_CHILD4_CASE(n, ...) \
+    case n: children_sums4<T, n>(__VA_ARGS__); break;
+#define PSIG_CHILDREN4(n, ...)                                                                               \
+    switch (n) {                                                                                             \
+        PSIG_CHILD4_CASE(2, __VA_ARGS__) PSIG_CHILD4_CASE(3, __VA_ARGS__) PSIG_CHILD4_CASE(4, __VA_ARGS__)   \
+        PSIG_CHILD4_CASE(5, __VA_ARGS__) PSIG_CHILD4_CASE(6, __VA_ARGS__) PSIG_CHILD4_CASE(7, __VA_ARGS__)   \
+        PSIG_CHILD4_CASE(8, __VA_ARGS__) PSIG_CHILD4_CASE(9, __VA_ARGS__) PSIG_CHILD4_CASE(10, __VA_ARGS__)  \
+        PSIG_CHILD4_CASE(11, __VA_ARGS__) PSIG_CHILD4_CASE(12, __VA_ARGS__)                                  \
+        default: break;                                                                                      \
+    }
 
 #define PSIG_CHILD_CASE(n, ...) \
     case n: children_sums<T, n>(__VA_ARGS__); break;
@@ -163,7 +209,7 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_FWD) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                       T *__restrict__ logsig)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -185,10 +231,24 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_forward
         if (p.top_words == nullptr && N >= 2) {
             // dense top degree: a thread takes a parent of degree N-1 and its d children
             const unsigned parents = p.dpow[N - 1];
+            // 4 scalars per access when the runs of d children start on such boundaries
+            const bool quads = (p.d & 3) == 0 && (p.lower & 3u) == 0 && (p.width & 3) == 0 &&
+                               (reinterpret_cast<uintptr_t>(sig) & (4 * sizeof(T) - 1)) == 0 &&
+                               (reinterpret_cast<uintptr_t>(logsig) & (4 * sizeof(T) - 1)) == 0;
             for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
                 const T *srun = s + p.lower + (size_t)u * p.d;
                 T *lrun = l + p.lower + (size_t)u * p.d;
-                PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
+                if (quads) {
+                    PSIG_CHILDREN4(N, p, xs, t1, u, [&](unsigned a, const T (&acc)[4]) {
+                        const Quad<T> in = *reinterpret_cast<const Quad<T> *>(srun + a);
+                        Quad<T> o;
+                        o.v[0] = in.v[0] + acc[0]; o.v[1] = in.v[1] + acc[1];
+                        o.v[2] = in.v[2] + acc[2]; o.v[3] = in.v[3] + acc[3];
+                        *reinterpret_cast<Quad<T> *>(lrun + a) = o;
+                    })
+                } else {
+                    PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
+                }
             }
         } else {
             for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
@@ -275,7 +335,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig)
 {
@@ -286,11 +346,13 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backwar
     T *ga = gx + p.lower;                      // adjoint of T_k
     T *gb = ga + p.lower;                      // adjoint of T_{k+1}
     T *tk = gb + p.lower;                      // every T_k (degrees 1..N-k) at t_off[k]
+    T *gts = tk + p.t_total;                   // dense top degree of the incoming gradient (when staged)
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
         const T *g = glog + row * p.width;
-        const T *gtop = g + p.lower;
+        const T *gtop_global = g + p.lower;
+        const T *gtop = p.stage_top ? gts : gtop_global;  // re-read N-1 times by each side of the adjoint
         T *out = gsig + row * p.width;
         __syncthreads();
         for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
@@ -302,7 +364,11 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backwar
             gb[i] = T(0);
         }
         // the top degree of x enters only through that same term
-        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) out[p.lower + i] = gtop[i];
+        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+            const T gi = gtop_global[i];
+            out[p.lower + i] = gi;
+            if (p.stage_top) gts[i] = gi;
+        }
         __syncthreads();
         build_t<T>(p, xs, ga, gb, tk);  // ends with a barrier
         const T *t1 = tk + p.t_off[1];
@@ -334,6 +400,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backwar
                         const unsigned run = p.dpow[N - m];
                         const T *grun = gtop + (size_t)(word - p.off[m]) * run;
                         const T *trun = t1 + p.off[N - m];
+#pragma unroll 4
                         for (unsigned v = lane; v < run; v += stride) acc = fma(grun[v], trun[v], acc);
                     }
                     if (team) {
@@ -356,6 +423,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB) logsig_backwar
                         const unsigned u0 = piece * 64u, u1 = min(du, u0 + 64u);
                         const T *xrun = xs + p.off[N - q];
                         T acc = T(0);
+#pragma unroll 4
                         for (unsigned u = u0; u < u1; ++u) acc = fma(xrun[u], gtop[(size_t)u * dq + v], acc);
                         atomicAdd(&ga[p.off[q] + v], acc);
                     }
@@ -431,11 +499,15 @@ int make_horner_plan(const PsigLogDesc &desc, const LevelTable &lt, HornerPlan *
         if (k <= lt.depth - 1) t += p.off[lt.depth - k + 1];
     }
     p.t_total = t;
+    p.stage_top = 0;
     return PSIG_OK;
 }
 
 template <typename T> size_t forward_smem(const HornerPlan &p) { return sizeof(T) * 3 * (size_t)p.lower; }
-template <typename T> size_t backward_smem(const HornerPlan &p) { return sizeof(T) * (5 * (size_t)p.lower + p.t_total); }
+template <typename T> size_t backward_smem(const HornerPlan &p)
+{
+    return sizeof(T) * (5 * (size_t)p.lower + p.t_total + (p.stage_top ? (size_t)p.top : 0));
+}
 
 unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : (1 << 20)); }
 
@@ -472,6 +544,9 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
     HornerPlan p;
     const int rc = make_horner_plan(desc, lt, &p);
     if (rc != PSIG_OK) return rc;
+    // a dense top degree is staged while the block stays under half of the largest supported footprint
+    p.stage_top = (p.top_words == nullptr && p.depth >= 2 &&
+                   sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top) <= kHornerMaxSmem / 2) ? 1u : 0u;
     const size_t smem = backward_smem<T>(p);
     auto kernel = logsig_backward_horner<T>;
     if (smem > 48 * 1024 &&
