@@ -26,9 +26,13 @@ namespace {
 #define PSIG_HORNER_BLOCK 256
 #endif
 constexpr int kHornerBlock = PSIG_HORNER_BLOCK;
-#ifndef PSIG_HORNER_MINB_FWD
-#define PSIG_HORNER_MINB_FWD 1
-#endif
+// Resident blocks per SM the forward kernel is compiled for.  A row is a chain of short phases with a
+// barrier each, so rows in flight per SM matter more than registers per thread (measured: 6 blocks
+// against 2 cut the forward time by 40 %); the values below are the largest that do not spill.
+template <typename T, int NMAX> constexpr int forward_blocks_per_sm()
+{
+    return sizeof(T) == 4 ? (NMAX <= 4 ? 8 : NMAX <= 8 ? 6 : 4) : 4;
+}
 #ifndef PSIG_HORNER_MINB_BWD
 #define PSIG_HORNER_MINB_BWD 1
 #endif
@@ -66,7 +70,8 @@ struct HornerPlan {
     unsigned dpow[kMaxDepth + 1];  // d^k (k < N; d^N only when it fits)
     unsigned t_off[kMaxDepth + 1];  // backward: start of T_k (degrees 1..N-k) in the T area
     unsigned t_total;
-    unsigned stage_top;  // backward: copy the dense top degree of the incoming gradient to shared memory
+    unsigned stage_top;  // backward: hold a dense image of the top degree of the incoming gradient in shared memory
+    unsigned top_dense;  // d^N (0 when it does not fit 31 bits)
 };
 
 // Four scalars moved as one access (16 bytes of float, 32 of double).
@@ -144,8 +149,10 @@ __device__ __forceinline__ void children_sums4(const HornerPlan &p, const T *xs,
     }
 }
 
+// NMAX (a template parameter of the enclosing function) bounds the depth an instance serves: deeper
+// cases are not instantiated, which keeps the registers of the shallow instances low.
 #define PSIG_CHILD4_CASE(n, ...) \
-    case n: children_sums4<T, n>(__VA_ARGS__); break;
+    case n: if constexpr (n <= NMAX) children_sums4<T, n>(__VA_ARGS__); break;
 #define PSIG_CHILDREN4(n, ...)                                                                               \
     switch (n) {                                                                                             \
         PSIG_CHILD4_CASE(2, __VA_ARGS__) PSIG_CHILD4_CASE(3, __VA_ARGS__) PSIG_CHILD4_CASE(4, __VA_ARGS__)   \
@@ -156,7 +163,7 @@ __device__ __forceinline__ void children_sums4(const HornerPlan &p, const T *xs,
     }
 
 #define PSIG_CHILD_CASE(n, ...) \
-    case n: children_sums<T, n>(__VA_ARGS__); break;
+    case n: if constexpr (n <= NMAX) children_sums<T, n>(__VA_ARGS__); break;
 // Dispatch on the children's degree (2..12).
 #define PSIG_CHILDREN(n, ...)                                                                             \
     switch (n) {                                                                                          \
@@ -169,7 +176,7 @@ __device__ __forceinline__ void children_sums4(const HornerPlan &p, const T *xs,
 
 // emit(position, sum) for every word of degree 2..M (position = its place in a dense row), the block's
 // threads taking parents in turn.  M <= N-1 here (words held in shared memory).
-template <typename T, class F>
+template <typename T, int NMAX, class F>
 __device__ __forceinline__ void for_words_below_top(const HornerPlan &p, int M, const T *xs, const T *ts, F &&emit)
 {
     if (M < 2) return;
@@ -184,7 +191,7 @@ __device__ __forceinline__ void for_words_below_top(const HornerPlan &p, int M, 
 // T_{N-1}, ..., T_1 in turn; T_k is built from T_{k+1} in the other buffer.  On return the result
 // T_1 (degrees 1..N-1) is in the buffer the function returns.  `keep`, when not null, receives a
 // copy of every T_k at keep + t_off[k].
-template <typename T>
+template <typename T, int NMAX>
 __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T *tb, T *keep)
 {
     const int N = p.depth;
@@ -197,7 +204,7 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
             nxt[i] = v;
             if (kept) kept[i] = v;
         }
-        for_words_below_top<T>(p, N - k, xs, cur, [&](unsigned pos, T acc) {
+        for_words_below_top<T, NMAX>(p, N - k, xs, cur, [&](unsigned pos, T acc) {
             const T v = -fma(xs[pos], c, acc);
             nxt[pos] = v;
             if (kept) kept[pos] = v;
@@ -208,8 +215,8 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
     return cur;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_FWD) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
+template <typename T, int NMAX>
+__global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                       T *__restrict__ logsig)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -223,11 +230,11 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_FWD) logsig_for
         __syncthreads();  // the previous row's readers are done with the buffers
         for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) xs[i] = s[i];
         __syncthreads();
-        const T *t1 = build_t<T>(p, xs, ta, tb, nullptr);
+        const T *t1 = build_t<T, NMAX>(p, xs, ta, tb, nullptr);
         // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
         if (N >= 2)
             for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) l[i] = xs[i];
-        for_words_below_top<T>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
+        for_words_below_top<T, NMAX>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
         if (p.top_words == nullptr && N >= 2) {
             // dense top degree: a thread takes a parent of degree N-1 and its d children
             const unsigned parents = p.dpow[N - 1];
@@ -334,7 +341,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
     }
 }
 
-template <typename T>
+template <typename T, int NMAX>
 __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig)
@@ -364,13 +371,22 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
             gb[i] = T(0);
         }
         // the top degree of x enters only through that same term
+        if (p.stage_top && p.top_words != nullptr) {
+            // a projected top degree is scattered into a dense image (zeros elsewhere), after which it
+            // goes through the same gathers as a dense one
+            for (unsigned i = threadIdx.x; i < p.top_dense; i += kHornerBlock) gts[i] = T(0);
+            __syncthreads();
+        }
         for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
             const T gi = gtop_global[i];
             out[p.lower + i] = gi;
-            if (p.stage_top) gts[i] = gi;
+            if (p.stage_top) {
+                if (p.top_words != nullptr) atomicAdd(&gts[(unsigned)p.top_words[i]], gi);  // a word may be listed twice
+                else gts[i] = gi;
+            }
         }
         __syncthreads();
-        build_t<T>(p, xs, ga, gb, tk);  // ends with a barrier
+        build_t<T, NMAX>(p, xs, ga, gb, tk);  // ends with a barrier
         const T *t1 = tk + p.t_off[1];
         for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) ga[i] = T(0);
         __syncthreads();
@@ -380,8 +396,8 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
         __syncthreads();
         // ---- the same product at the top degree ----
         if (N >= 2) {
-            if (p.top_words == nullptr) {
-                // dense: gx[u] += sum_v gtop[u.v] T_1(v), a warp per u while the run is long
+            if (p.top_words == nullptr || p.stage_top) {
+                // dense (or its image): gx[u] += sum_v gtop[u.v] T_1(v), a warp per u while the run is long
                 const unsigned long_words = [&] {
                     unsigned w = 0;
                     for (int m = 1; m <= N - 1; ++m)
@@ -491,6 +507,7 @@ int make_horner_plan(const PsigLogDesc &desc, const LevelTable &lt, HornerPlan *
     if (pw * (unsigned long long)lt.d > 0x7fffffffULL) return PSIG_ERR_UNSUPPORTED;
     if (lt.size[lt.depth] > 0x7fffffffLL) return PSIG_ERR_UNSUPPORTED;
     p.top = (unsigned)lt.size[lt.depth];
+    p.top_dense = (unsigned)(pw * (unsigned long long)lt.d);
     p.top_words = lt.words[lt.depth];
     if ((long long)p.lower + (long long)p.top != lt.total) return PSIG_ERR_UNSUPPORTED;  // lower degrees must be dense
     unsigned t = 0;
@@ -506,7 +523,7 @@ int make_horner_plan(const PsigLogDesc &desc, const LevelTable &lt, HornerPlan *
 template <typename T> size_t forward_smem(const HornerPlan &p) { return sizeof(T) * 3 * (size_t)p.lower; }
 template <typename T> size_t backward_smem(const HornerPlan &p)
 {
-    return sizeof(T) * (5 * (size_t)p.lower + p.t_total + (p.stage_top ? (size_t)p.top : 0));
+    return sizeof(T) * (5 * (size_t)p.lower + p.t_total + (p.stage_top ? (size_t)p.top_dense : 0));
 }
 
 unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : (1 << 20)); }
@@ -529,12 +546,17 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
     const int rc = make_horner_plan(desc, lt, &p);
     if (rc != PSIG_OK) return rc;
     const size_t smem = forward_smem<T>(p);
-    auto kernel = logsig_forward_horner<T>;
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return PSIG_ERR_CUDA;
-    kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
-    return check_launch();
+    auto launch = [&](auto kernel) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)PSIG_ERR_CUDA;
+        kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
+        return check_launch();
+    };
+    if (p.depth <= 4) return launch(logsig_forward_horner<T, 4>);
+    if (p.depth <= 6) return launch(logsig_forward_horner<T, 6>);
+    if (p.depth <= 8) return launch(logsig_forward_horner<T, 8>);
+    return launch(logsig_forward_horner<T, 12>);
 }
 
 template <typename T>
@@ -544,16 +566,22 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
     HornerPlan p;
     const int rc = make_horner_plan(desc, lt, &p);
     if (rc != PSIG_OK) return rc;
-    // a dense top degree is staged while the block stays under half of the largest supported footprint
-    p.stage_top = (p.top_words == nullptr && p.depth >= 2 &&
-                   sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top) <= kHornerMaxSmem / 2) ? 1u : 0u;
+    // the top degree is staged (dense, or as a dense image of the listed words) while the block stays
+    // under half of the largest supported footprint
+    p.stage_top = (p.depth >= 2 &&
+                   sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top_dense) <= kHornerMaxSmem / 2) ? 1u : 0u;
     const size_t smem = backward_smem<T>(p);
-    auto kernel = logsig_backward_horner<T>;
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return PSIG_ERR_CUDA;
-    kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
-    return check_launch();
+    auto launch = [&](auto kernel) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)PSIG_ERR_CUDA;
+        kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
+        return check_launch();
+    };
+    if (p.depth <= 4) return launch(logsig_backward_horner<T, 4>);
+    if (p.depth <= 6) return launch(logsig_backward_horner<T, 6>);
+    if (p.depth <= 8) return launch(logsig_backward_horner<T, 8>);
+    return launch(logsig_backward_horner<T, 12>);
 }
 
 template int horner_logsig_backward<float>(const PsigLogDesc &, const LevelTable &, const float *, const float *,
