@@ -42,9 +42,9 @@ UNIT = "paths*steps/s"
 # DRAM traffic of one launch of the dominant kernel, from ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
 NCU_TRAFFIC_BYTES = {
-    # sig_backward_tiled at (8,4): 178.95 MB captured at B=128 (profiles/sig_backward_tiled_d8_n4_cfg2_b128.md),
+    # sig_backward_tiled at (8,4): 180.6 MB captured at B=128 (profiles/sig_backward_tiled_d8_n4_cfg2_b128.md),
     # proportional in units -> B=256
-    "cfg2": 357.9e6,
+    "cfg2": 361.3e6,
 }
 
 
