@@ -133,7 +133,11 @@ int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool tiled = use_tiled(desc, &rc);
     if (rc != PSIG_OK) return rc;
-    if (tiled) return tiled_sig_forward(*desc, static_cast<const float *>(path), static_cast<float *>(out), st);
+    if (tiled) {
+        if (desc->dtype == PSIG_F32)
+            return tiled_sig_forward<float>(*desc, static_cast<const float *>(path), static_cast<float *>(out), st);
+        return tiled_sig_forward<double>(*desc, static_cast<const double *>(path), static_cast<double *>(out), st);
+    }
     if (desc->dtype == PSIG_F32)
         return generic_sig_forward<float>(*desc, lt, static_cast<const float *>(path), static_cast<float *>(out), st);
     return generic_sig_forward<double>(*desc, lt, static_cast<const double *>(path), static_cast<double *>(out), st);
@@ -165,9 +169,15 @@ int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool tiled = use_tiled(desc, &rc);
     if (rc != PSIG_OK) return rc;
-    if (tiled)
-        return tiled_sig_backward(*desc, static_cast<const float *>(path), static_cast<const float *>(sig),
-                                  static_cast<const float *>(grad_sig), static_cast<float *>(grad_path), workspace, st);
+    if (tiled) {
+        if (desc->dtype == PSIG_F32)
+            return tiled_sig_backward<float>(*desc, static_cast<const float *>(path), static_cast<const float *>(sig),
+                                             static_cast<const float *>(grad_sig), static_cast<float *>(grad_path),
+                                             workspace, st);
+        return tiled_sig_backward<double>(*desc, static_cast<const double *>(path), static_cast<const double *>(sig),
+                                          static_cast<const double *>(grad_sig), static_cast<double *>(grad_path),
+                                          workspace, st);
+    }
     if (desc->dtype == PSIG_F32)
         return generic_sig_backward<float>(*desc, lt, static_cast<const float *>(path),
                                            static_cast<const float *>(sig), static_cast<const float *>(grad_sig),

@@ -58,13 +58,15 @@ template <typename T>
 int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *grad_logsig,
                            T *grad_sig, cudaStream_t stream);
 
-// Register-tiled dense float32 kernels (tiled_sig.cu).  `supported` tells whether a kernel
+// Register-tiled dense kernels, float32 and float64 (tiled_sig.cu).  `supported` tells whether a kernel
 // exists for this description (dense, or dense below a projected top degree).
 bool tiled_supported(const PsigSigDesc &desc);
-int tiled_sig_forward(const PsigSigDesc &desc, const float *path, float *out, cudaStream_t stream);
+template <typename T>
+int tiled_sig_forward(const PsigSigDesc &desc, const T *path, T *out, cudaStream_t stream);
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
-int tiled_sig_backward(const PsigSigDesc &desc, const float *path, const float *sig, const float *grad,
-                       float *grad_path, void *workspace, cudaStream_t stream);
+template <typename T>
+int tiled_sig_backward(const PsigSigDesc &desc, const T *path, const T *sig, const T *grad, T *grad_path,
+                       void *workspace, cudaStream_t stream);
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? PSIG_OK : PSIG_ERR_CUDA; }
 

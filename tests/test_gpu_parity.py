@@ -204,7 +204,7 @@ def test_reference_build_agrees(ps, oracle):
         assert util.rel_error(ours_gs, theirs_gs) < util.TOL[dtype]
 
 
-# ---- register-tiled kernels (float32, dense) ----
+# ---- register-tiled kernels (dense, or dense below a projected top degree) ----
 
 TILED = [(8, 4), (16, 4), (16, 3), (4, 6),
          (3, 5), (3, 6), (3, 7), (4, 4), (4, 5), (4, 7), (5, 4), (5, 5), (5, 6), (6, 4), (6, 5),
@@ -214,16 +214,18 @@ TILED_PROJECTED_TOP = [(4, 6), (8, 4), (16, 3), (3, 5), (3, 6), (3, 7), (4, 4), 
                        (6, 5), (8, 3), (10, 3), (12, 3), (16, 2), (32, 2)]
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("d,depth", TILED)
 @pytest.mark.parametrize("L", [2, 3, 34, 101])
-def test_tiled_signature(ps, oracle, d, depth, L):
-    x = util.brownian_path(3, L, d, seed=L + d, dtype=torch.float32)
+def test_tiled_signature(ps, oracle, d, depth, L, dtype):
+    x = util.brownian_path(3, L, d, seed=L + d, dtype=dtype)
     _run_sig(ps, oracle, x, depth, algo="tiled")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("d,depth", TILED)
-def test_tiled_windows(ps, oracle, d, depth):
-    x = util.brownian_path(2, 70, d, seed=d, dtype=torch.float32)
+def test_tiled_windows(ps, oracle, d, depth, dtype):
+    x = util.brownian_path(2, 70, d, seed=d, dtype=dtype)
     win = torch.tensor([[0, 70], [5, 7], [10, 50], [3, 3], [12, 13], [20, 70], [0, 41], [33, 66]], dtype=torch.int32)
     _run_sig(ps, oracle, x, depth, windows=win, algo="tiled")
 
@@ -237,14 +239,15 @@ def test_tiled_unsupported_shape_is_an_error(ps):
         ps.ops.set_algorithm("auto")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("d,depth", TILED_PROJECTED_TOP)
 @pytest.mark.parametrize("windowed", [False, True])
-def test_tiled_projected_top_degree(ps, oracle, d, depth, windowed):
+def test_tiled_projected_top_degree(ps, oracle, d, depth, windowed, dtype):
     """Dense degrees below a projected top degree (the LogSignature layout) on the tiled kernels."""
     top = util.random_words(37, d, depth, depth, seed=d)
     proj = ps.projections.words(top, depth, d, full_levels=tuple(range(1, depth)))
     assert proj.level_sizes[depth] == 37
-    x = util.brownian_path(3, 45, d, seed=3 * d, dtype=torch.float32)
+    x = util.brownian_path(3, 45, d, seed=3 * d, dtype=dtype)
     win = util.sliding_windows(45, 20, 9) if windowed else None
     _run_sig(ps, oracle, x, depth, proj=proj, windows=win, algo="tiled")
     _run_sig(ps, oracle, x, depth, proj=proj, windows=win, algo="generic")
