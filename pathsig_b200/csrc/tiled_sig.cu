@@ -1,8 +1,8 @@
-// Register-tiled dense signature kernels (float32, compile-time channel count D and depth N).
+// Register-tiled dense signature kernels (compile-time channel count D and depth N).
 //
 // The word tree is cut at a prefix length P.  One thread owns a prefix u (|u| = P) and, of the
 // sub-tree below it, the DA first letters [a0, a0+DA): the values S(u.a), S(u.a.b), ... down
-// to degree N live in registers (DA * (1 + D + ... ) floats), the P values S(u[:j]) on the
+// to degree N live in registers (DA * (1 + D + ... ) scalars), the P values S(u[:j]) on the
 // way to the root are kept redundantly by every thread that shares them.  One step of Chen's
 // recurrence S <- S (x) exp(dx) is then, per target degree k, a Horner chain
 //     B_j = B_{j-1} * dx[w_j] / (k-j+1) + S_j         (j = 1..k-1),   S_k += B_{k-1} * dx[w_k]
@@ -10,8 +10,8 @@
 // sub-tree: no shared-memory state, no barrier and no shuffle inside the step loop.  Shared
 // prefixes are evaluated once per thread instead of once per word as in the reference
 // (src/pathsig/forward/sig_kernels.cu:138-152), which is where the ~8x arithmetic saving at
-// (d, depth) = (8, 4) comes from.  Increments (and their multiples 1/2, 1/3 needed by the
-// Horner tail) are staged in shared memory a chunk of steps at a time.
+// (d, depth) = (8, 4) comes from.  Increments are staged in shared memory a chunk of steps at a
+// time; the factors 1/2, 1/3 of the Horner tail ride on the scalar multiplier.
 //
 // Backward is reverse-mode through the same recurrence.  Going back one step, degrees are
 // visited bottom-up: the Horner values are rebuilt from the already rolled-back lower
