@@ -174,6 +174,11 @@ def test_fake_operators_give_reference_shapes():
     assert ps.ops.logsig_backward(sig, cache, sig, 4, False, ew, [0, 8, 64, 512, 4096]).shape == sig.shape
     with pytest.raises(RuntimeError):
         ps.ops.compute_signature(torch.empty(2, 1, 3, device="meta"), 2, False, ew, [], False, nowin)
+    # Chen product and its adjoint keep the shape of their operands
+    a = torch.empty(5, 7, 4680, device="meta")
+    assert ps.ops.chen_product(a, a, 4, 8).shape == a.shape
+    ga, gb = ps.ops.chen_product_backward(a, a, a, 4, 8)
+    assert ga.shape == a.shape and gb.shape == a.shape
 
 
 def test_cpu_tensors_are_refused():
