@@ -628,7 +628,9 @@ def run_ours(args):
             B = None
             if other == "cfg5":
                 B = SPECS["cfg5"]["B"] // world  # strong scaling: the 4096 paths are sharded over the ranks
-            r = measure_workload(other, max(3, min(args.steps, 5)), 2, world, device, per_rank_B=B, fp32_peak=fp32_peak)
+            # short runs: 3 warm-up steps, then 20 timed steps of the sub-millisecond workloads, 5 of config 5
+            n_other = max(3, min(args.steps, 5 if other == "cfg5" else 20))
+            r = measure_workload(other, n_other, 3, world, device, per_rank_B=B, fp32_peak=fp32_peak)
             r.pop("_wl")
             if other == "cfg5":
                 r["scaling"] = "strong"

@@ -778,10 +778,15 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
         const unsigned block = 32u * lw;
         const size_t smem = sizeof(T) * 32 * (size_t)plan.lane_stride;
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
-        if (single && shallow) sig_forward_lanes<T, 1, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, out);
-        else if (single) sig_forward_lanes<T, 1, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, out);
-        else if (shallow) sig_forward_lanes<T, TB, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, out);
-        else sig_forward_lanes<T, TB, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, out);
+        auto launch = [&](auto kernel) {
+            // the staged increments make shared memory the occupancy limit under the default L1 split
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            kernel<<<grid, block, smem, stream>>>(plan, path, out);
+        };
+        if (single && shallow) launch(sig_forward_lanes<T, 1, kLaneShallow>);
+        else if (single) launch(sig_forward_lanes<T, 1, kMaxDepth>);
+        else if (shallow) launch(sig_forward_lanes<T, TB, kLaneShallow>);
+        else launch(sig_forward_lanes<T, TB, kMaxDepth>);
         return check_launch();
     }
     const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));
@@ -811,14 +816,17 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
         const unsigned block = 32u * lw;
         const size_t smem = 2 * sizeof(T) * 32 * (size_t)plan.lane_stride;
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
-        if (single && shallow)
-            sig_backward_lanes<T, 1, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
-        else if (single)
-            sig_backward_lanes<T, 1, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
-        else if (shallow)
-            sig_backward_lanes<T, TB, kLaneShallow><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
-        else
-            sig_backward_lanes<T, TB, kMaxDepth><<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        auto launch = [&](auto kernel) {
+            if (smem > 48 * 1024 &&
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                return;  // the launch below then fails and reports the error
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            kernel<<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
+        };
+        if (single && shallow) launch(sig_backward_lanes<T, 1, kLaneShallow>);
+        else if (single) launch(sig_backward_lanes<T, 1, kMaxDepth>);
+        else if (shallow) launch(sig_backward_lanes<T, TB, kLaneShallow>);
+        else launch(sig_backward_lanes<T, TB, kMaxDepth>);
         if (check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
     } else if (units > 0 && blocks > 0) {
         const dim3 grid((unsigned)blocks, (unsigned)(units < 65535 ? units : 65535));

@@ -550,6 +550,8 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
         if (smem > 48 * 1024 &&
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return (int)PSIG_ERR_CUDA;
+        // rows in flight are limited by shared memory under the default L1 split
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
         return check_launch();
     };
@@ -575,6 +577,7 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
         if (smem > 48 * 1024 &&
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return (int)PSIG_ERR_CUDA;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
         return check_launch();
     };
