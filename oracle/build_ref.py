@@ -5,8 +5,8 @@ strongest parity pin there is: the GPU tests load this library next to ours (its
 live in ``torch.ops.pathsig``, ours in ``torch.ops.pathsig_b200``) and compare outputs on the
 same tensors, and ``tests/golden/make_golden.py`` records its outputs as fixtures.
 
-The sources are compiled where they lie (``$PATHSIG_REFERENCE_ROOT``, default
-``/root/reference``) with plain nvcc commands; the reference's own CMake build is not run and
+The sources are compiled where they lie (the checkout named by ``$PATHSIG_REFERENCE_ROOT``, or
+the default location of ``reference_root()``) with plain nvcc commands; the reference's own CMake build is not run and
 no source file is copied.  Outputs go to ``oracle/_ref/`` only, which git ignores.  When the
 reference tree is absent (for example on a GPU box) the function leaves an existing library
 alone and reports whether one is there.

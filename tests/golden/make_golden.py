@@ -3,9 +3,9 @@
 Run on a machine with a CUDA GPU after ``python oracle/build_ref.py`` has produced
 ``oracle/_ref/libpathsig_ops.so`` (the reference's unchanged sources compiled with nvcc):
 
-    python tests/golden/make_golden.py --out gpurun_out/golden_reference.pt
+    python tests/golden/make_golden.py
 
-and copy the file to ``tests/golden/golden_reference.pt``.  Each case stores its inputs, the
+which rewrites ``tests/golden/golden_reference.pt``.  Each case stores its inputs, the
 operator arguments and the reference's outputs, so the consumers (tests/test_golden.py) need
 neither the reference nor a GPU.  Only ``torch.ops.pathsig.*`` of the reference library is
 called here; projections are described by explicit code lists.
@@ -31,7 +31,7 @@ def lyndon_codes(d, n):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "golden_reference.pt"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "golden_reference.pt"))
     args = ap.parse_args()
     ref = util.reference_ops()
     if ref is None:
