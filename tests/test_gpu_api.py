@@ -205,3 +205,26 @@ def test_cuda_graph_capture_and_replay(ps):
     torch.testing.assert_close(out_g, ref_out, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(grad_g, ref_grad, rtol=1e-4, atol=1e-5)
     assert not torch.allclose(ref_out, want_out)
+
+
+def test_traced_by_torch_compile(ps):
+    """The operators trace under torch.compile (fake implementations + registered autograd): a compiled
+    function gives the eager result, forward and backward, without graph breaks."""
+    win = torch.tensor([[0, 12], [5, 20]], dtype=torch.int32, device=DEV)
+    sig = ps.Signature(depth=3, windows=win)
+    logsig = ps.LogSignature(depth=4, projection=ps.projections.lyndon(4, 3))
+
+    def fn(x):
+        a = sig(x)
+        b = logsig(x)
+        c = ps.chen_product(a[:, 0], a[:, 1], path_dim=3, depth=3)
+        return a.square().sum() + b.sum() + c.sum()
+
+    compiled = torch.compile(fn, backend="aot_eager", fullgraph=True)
+    x1 = _path(3, 20, 3).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    y1, y2 = fn(x1), compiled(x2)
+    y1.backward()
+    y2.backward()
+    assert torch.allclose(y1, y2, rtol=1e-12, atol=0)
+    assert torch.allclose(x1.grad, x2.grad, rtol=1e-10, atol=1e-12)
