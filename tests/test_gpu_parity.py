@@ -208,10 +208,12 @@ def test_reference_build_agrees(ps, oracle):
 
 TILED = [(8, 4), (16, 4), (16, 3), (4, 6),
          (3, 5), (3, 6), (3, 7), (4, 4), (4, 5), (4, 7), (5, 4), (5, 5), (5, 6), (6, 4), (6, 5),
-         (8, 3), (8, 5), (8, 6), (10, 3), (10, 4), (12, 3), (16, 2), (32, 2), (32, 3)]
+         (8, 3), (8, 5), (8, 6), (10, 3), (10, 4), (12, 3), (16, 2), (32, 2), (32, 3),
+         (2, 8), (2, 10), (5, 3), (6, 3), (6, 6), (7, 3), (7, 4), (9, 3), (9, 4), (12, 4), (20, 3)]
 # shapes whose unit is one thread block and whose top degree fits the shared-memory staging
 TILED_PROJECTED_TOP = [(4, 6), (8, 4), (16, 3), (3, 5), (3, 6), (3, 7), (4, 4), (4, 5), (5, 4), (5, 5), (6, 4),
-                       (6, 5), (8, 3), (10, 3), (12, 3), (16, 2), (32, 2)]
+                       (6, 5), (8, 3), (10, 3), (12, 3), (16, 2), (32, 2),
+                       (2, 8), (2, 10), (5, 3), (6, 3), (7, 3), (7, 4), (9, 3), (9, 4), (20, 3)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
@@ -234,7 +236,7 @@ def test_tiled_unsupported_shape_is_an_error(ps):
     ps.ops.set_algorithm("tiled")
     try:
         with pytest.raises(RuntimeError):
-            ps.Signature(depth=5)(torch.zeros(1, 4, 7, device=DEV))
+            ps.Signature(depth=5)(torch.zeros(1, 4, 11, device=DEV))
     finally:
         ps.ops.set_algorithm("auto")
 
