@@ -228,3 +228,38 @@ def test_traced_by_torch_compile(ps):
     y2.backward()
     assert torch.allclose(y1, y2, rtol=1e-12, atol=0)
     assert torch.allclose(x1.grad, x2.grad, rtol=1e-10, atol=1e-12)
+
+
+def test_concurrent_host_threads_and_streams(ps):
+    """The operators are re-entrant: four host threads, each on its own stream and its own shape, get the
+    results a single thread gets (the reference's launchers are re-entrant too, guarded per device)."""
+    import threading
+
+    shapes = [(8, 4, False), (3, 5, False), (5, 3, True), (4, 6, True)]  # (d, depth, log-signature)
+    inputs = [_path(6, 40 + 3 * i, d, seed=i) for i, (d, _, _) in enumerate(shapes)]
+
+    def work(i, stream, out):
+        d, depth, log = shapes[i]
+        mod = ps.LogSignature(depth=depth) if log else ps.Signature(depth=depth)
+        with torch.cuda.stream(stream):
+            for _ in range(5):
+                x = inputs[i].clone().requires_grad_(True)
+                y = mod(x)
+                y.square().sum().backward()
+            out[i] = (y.detach(), x.grad)
+            stream.synchronize()
+
+    serial, threaded = {}, {}
+    for i in range(len(shapes)):
+        work(i, torch.cuda.current_stream(), serial)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in shapes]
+    threads = [threading.Thread(target=work, args=(i, streams[i], threaded)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    for i in range(len(shapes)):
+        assert util.rel_error(threaded[i][0], serial[i][0]) < 1e-12
+        assert util.rel_error(threaded[i][1], serial[i][1]) < 1e-11
