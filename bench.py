@@ -389,20 +389,37 @@ def reference_cuda_baseline(wl, device, steps=5, warmup=2):
     """The reference's own CUDA operators (built unchanged into oracle/_ref/ by oracle/build_ref.py)
     on the same tensors, as a reported baseline.  Returns None when that library is not there."""
     lib = os.path.join(ROOT, "oracle", "_ref", "libpathsig_ops.so")
-    if not os.path.isfile(lib) or wl.spec["kind"] == "loglyndon":
+    if not os.path.isfile(lib):
         return None
     try:
         torch.ops.load_library(lib)
         ref = torch.ops.pathsig
         m = wl.mod
-        args = (m.depth, m.alternative_projection, m._encoded_words, list(m._level_sizes), m.use_windows, m._windows)
+        if wl.spec["kind"] == "loglyndon":
+            # the reference's LogSignature: signature in the hybrid layout -> logarithm -> column selection
+            d, ls, tw, idx = wl.d, list(m._ext_level_sizes), m._top_words, m._indices_from_sig
+            sargs = (m.depth, m.alternative_projection, tw, ls, m.use_windows, m._windows)
+            largs = (m.depth, m.alternative_projection, tw, ls)
 
-        def fwd():
-            return ref.compute_signature(wl.x, *args)
+            def fwd():
+                sig = ref.compute_signature(wl.x, *sargs)
+                logsig, cache = ref.sig_to_logsig(sig, m.depth, d, m.alternative_projection, tw, ls)
+                return sig, logsig, cache, logsig.index_select(-1, idx)
 
-        def fwd_bwd():
-            sig = ref.compute_signature(wl.x, *args)
-            return ref.signature_backward(wl.x, sig, wl.G, *args)
+            def fwd_bwd():
+                sig, logsig, cache, _ = fwd()
+                g_full = torch.zeros_like(logsig).index_add_(-1, idx, wl.G)
+                g_sig = ref.logsig_backward(sig, cache, g_full, *largs)
+                return ref.signature_backward(wl.x, sig, g_sig, *sargs)
+        else:
+            args = (m.depth, m.alternative_projection, m._encoded_words, list(m._level_sizes), m.use_windows, m._windows)
+
+            def fwd():
+                return ref.compute_signature(wl.x, *args)
+
+            def fwd_bwd():
+                sig = ref.compute_signature(wl.x, *args)
+                return ref.signature_backward(wl.x, sig, wl.G, *args)
 
         ms_f = time_steps(fwd, steps, warmup, 1, device)
         ms_fb = time_steps(fwd_bwd, steps, warmup, 1, device)
@@ -631,7 +648,13 @@ def run_ours(args):
             # short runs: 3 warm-up steps, then 20 timed steps of the sub-millisecond workloads, 5 of config 5
             n_other = max(3, min(args.steps, 5 if other == "cfg5" else 20))
             r = measure_workload(other, n_other, 3, world, device, per_rank_B=B, fp32_peak=fp32_peak)
-            r.pop("_wl")
+            other_wl = r.pop("_wl")
+            if rank == 0 and world == 1 and not args.no_cpu:
+                # the reference's CUDA operators on the same tensors (one timed step of config 5: it runs for seconds)
+                few = other == "cfg5"
+                r["reference_cuda"] = reference_cuda_baseline(other_wl, device, steps=1 if few else 5,
+                                                              warmup=1 if few else 2)
+            del other_wl
             if other == "cfg5":
                 r["scaling"] = "strong"
             others[other] = r
