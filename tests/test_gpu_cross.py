@@ -43,7 +43,7 @@ def _windows(rng, L, W):
     return torch.tensor(rows, dtype=torch.int32, device=DEV)
 
 
-@pytest.mark.parametrize("seed", range(48))
+@pytest.mark.parametrize("seed", range(140))
 def test_tiled_agrees_with_generic(ps, seed):
     rng = random.Random(1000 + seed)
     d, depth = TILED[seed % len(TILED)]
@@ -73,7 +73,7 @@ def test_tiled_agrees_with_generic(ps, seed):
     assert util.rel_error(grad_t, grad_g) < tol
 
 
-@pytest.mark.parametrize("seed", range(17))
+@pytest.mark.parametrize("seed", range(52))
 def test_tiled_projected_top_agrees_with_generic(ps, seed):
     rng = random.Random(2000 + seed)
     d, depth = TILED_PROJECTED_TOP[seed % len(TILED_PROJECTED_TOP)]
@@ -98,7 +98,7 @@ def test_tiled_projected_top_agrees_with_generic(ps, seed):
     assert util.rel_error(grad_t, grad_g) < tol
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(60))
 def test_log_kernel_families_agree(ps, seed):
     rng = random.Random(3000 + seed)
     d = rng.choice([1, 2, 3, 4, 5, 7, 8])
