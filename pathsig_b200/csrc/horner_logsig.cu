@@ -151,6 +151,39 @@ __device__ __forceinline__ void children_sums4(const HornerPlan &p, const T *xs,
 
 // NMAX (a template parameter of the enclosing function) bounds the depth an instance serves: deeper
 // cases are not instantiated, which keeps the registers of the shallow instances low.
+// One quad of children (a, a+1, a+2, a+3) of parent u: the unit of work when the threads of a warp take
+// neighbouring quads, so that their 16-byte shared-memory reads and global accesses are consecutive
+// (a thread looping over all children of its own parent reads at a stride of d scalars instead, which
+// is an 8-way bank conflict at d = 8).  Needs d % 4 == 0.
+template <typename T, int NDEG>
+__device__ __forceinline__ void quad_sums(const HornerPlan &p, const T *xs, const T *ts, unsigned u, unsigned a,
+                                          T (&acc)[4])
+{
+    unsigned q = u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = T(0);
+#pragma unroll
+    for (int lp = 0; lp <= NDEG - 2; ++lp) {
+        const unsigned rem = u - q * p.dpow[lp];
+        const T xp = xs[p.off[NDEG - 1 - lp] + q];
+        const Quad<T> tq = *reinterpret_cast<const Quad<T> *>(ts + p.off[lp + 1] + rem * (unsigned)p.d + a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fma(xp, tq.v[i], acc[i]);
+        q = p.by_d.div(q);
+    }
+}
+
+#define PSIG_QUAD_CASE(n, ...) \
+    case n: if constexpr (n <= NMAX) quad_sums<T, n>(__VA_ARGS__); break;
+#define PSIG_QUAD(n, ...)                                                                              \
+    switch (n) {                                                                                       \
+        PSIG_QUAD_CASE(2, __VA_ARGS__) PSIG_QUAD_CASE(3, __VA_ARGS__) PSIG_QUAD_CASE(4, __VA_ARGS__)   \
+        PSIG_QUAD_CASE(5, __VA_ARGS__) PSIG_QUAD_CASE(6, __VA_ARGS__) PSIG_QUAD_CASE(7, __VA_ARGS__)   \
+        PSIG_QUAD_CASE(8, __VA_ARGS__) PSIG_QUAD_CASE(9, __VA_ARGS__) PSIG_QUAD_CASE(10, __VA_ARGS__)  \
+        PSIG_QUAD_CASE(11, __VA_ARGS__) PSIG_QUAD_CASE(12, __VA_ARGS__)                                \
+        default: break;                                                                                \
+    }
+
 #define PSIG_CHILD4_CASE(n, ...) \
     case n: if constexpr (n <= NMAX) children_sums4<T, n>(__VA_ARGS__); break;
 #define PSIG_CHILDREN4(n, ...)                                                                               \
@@ -242,18 +275,24 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
             const bool quads = (p.d & 3) == 0 && (p.lower & 3u) == 0 && (p.width & 3) == 0 &&
                                (reinterpret_cast<uintptr_t>(sig) & (4 * sizeof(T) - 1)) == 0 &&
                                (reinterpret_cast<uintptr_t>(logsig) & (4 * sizeof(T) - 1)) == 0;
-            for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
-                const T *srun = s + p.lower + (size_t)u * p.d;
-                T *lrun = l + p.lower + (size_t)u * p.d;
-                if (quads) {
-                    PSIG_CHILDREN4(N, p, xs, t1, u, [&](unsigned a, const T (&acc)[4]) {
-                        const Quad<T> in = *reinterpret_cast<const Quad<T> *>(srun + a);
-                        Quad<T> o;
-                        o.v[0] = in.v[0] + acc[0]; o.v[1] = in.v[1] + acc[1];
-                        o.v[2] = in.v[2] + acc[2]; o.v[3] = in.v[3] + acc[3];
-                        *reinterpret_cast<Quad<T> *>(lrun + a) = o;
-                    })
-                } else {
+            if (quads) {
+                // a thread takes one quad of children; neighbouring threads take neighbouring quads
+                const unsigned per_parent = (unsigned)p.d / 4u, items = parents * per_parent;
+                for (unsigned it = threadIdx.x; it < items; it += kHornerBlock) {
+                    const unsigned u = it / per_parent, a = 4u * (it - u * per_parent);
+                    T acc[4];
+                    PSIG_QUAD(N, p, xs, t1, u, a, acc)
+                    const size_t pos = p.lower + (size_t)u * p.d + a;
+                    const Quad<T> in = *reinterpret_cast<const Quad<T> *>(s + pos);
+                    Quad<T> o;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o.v[i] = in.v[i] + acc[i];
+                    *reinterpret_cast<Quad<T> *>(l + pos) = o;
+                }
+            } else {
+                for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
+                    const T *srun = s + p.lower + (size_t)u * p.d;
+                    T *lrun = l + p.lower + (size_t)u * p.d;
                     PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
                 }
             }
