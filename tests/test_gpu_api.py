@@ -263,3 +263,28 @@ def test_concurrent_host_threads_and_streams(ps):
     for i in range(len(shapes)):
         assert util.rel_error(threaded[i][0], serial[i][0]) < 1e-12
         assert util.rel_error(threaded[i][1], serial[i][1]) < 1e-11
+
+
+@pytest.mark.parametrize("d,depth,B,L,dtype,log", [
+    (3, 3, 70000, 4, torch.float32, False),   # lane kernels, more unit groups than one grid dimension holds
+    (8, 4, 70000, 3, torch.float32, False),   # tiled kernels, 70 000 blocks
+    (2, 2, 200000, 2, torch.float64, False),
+    (4, 3, 70000, 5, torch.float32, True),    # log-signature rows beyond 65 535
+])
+def test_batches_beyond_grid_limits(ps, d, depth, B, L, dtype, log):
+    """The reference maps batch and windows to grid.y / grid.z and so stops at 65 535 of each
+    (src/pathsig/forward/sig_launch.cu:47); here sampled rows of a larger batch equal the same rows
+    computed on their own."""
+    x = _path(B, L, d, seed=B % 97, dtype=dtype)
+    mod = (ps.LogSignature if log else ps.Signature)(depth=depth)
+    xg = x.clone().requires_grad_(True)
+    out = mod(xg)
+    out.square().sum().backward()
+    rows = torch.tensor([0, 1, B // 2, 65535, 65536, B - 1], device=DEV)
+    xs = x[rows].clone().requires_grad_(True)
+    sub = mod(xs)
+    sub.square().sum().backward()
+    tol = 2e-5 if dtype == torch.float32 else 1e-11
+    assert torch.isfinite(out).all() and torch.isfinite(xg.grad).all()
+    assert util.rel_error(out[rows], sub) < tol
+    assert util.rel_error(xg.grad[rows], xs.grad) < tol
