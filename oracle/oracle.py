@@ -12,7 +12,8 @@ operators of the reference (``src/pathsig/bindings.cpp:9-63``):
 * :func:`logsig_backward`   ~ ``pathsig::logsig_backward``
 
 plus :func:`logsignature`, which chains them the way ``LogSignature.forward`` does
-(``src/pathsig/modules.py:112-135``).
+(``src/pathsig/modules.py:112-135``), and :func:`chen_product`, a definition-level statement (torch
+outer products, no native code) of the one operator of the package that the reference does not have.
 """
 from __future__ import annotations
 
@@ -197,3 +198,47 @@ def logsignature(path, depth, *, top_words=None, ext_level_sizes=None, indices=N
     gpath = sig_backward(path, sig, gsig, depth, top_words if projected else None,
                          ext_level_sizes if projected else None, windows)
     return out, gpath
+
+
+def chen_product(sig_a, sig_b, d: int, depth: int):
+    """Truncated tensor product of two dense signatures ``(..., D)`` (degree-0 coordinate 1 implied):
+    ``out_n = a_n + b_n + sum_{0<k<n} a_k (x) b_{n-k}``, level by level with explicit outer products.
+
+    Not an operator of the reference (it never combines signatures); the definition is Chen's identity
+    for the signature of a concatenation, which the reference's forward recurrence applies one
+    increment at a time (``src/pathsig/forward/sig_kernels.cu:138-152``).  Returns
+    ``(out, grad_fn)`` where ``grad_fn(g)`` gives ``(dL/da, dL/db)`` for ``dL/dout = g``.
+    """
+    a, b = _cpu(sig_a, torch.float64), _cpu(sig_b, torch.float64)
+    lead = a.shape[:-1]
+    off = [0]
+    for k in range(1, depth + 1):
+        off.append(off[-1] + d ** k)
+    if a.shape[-1] != off[-1] or b.shape != a.shape:
+        raise ValueError("signatures must be dense rows of equal shape")
+    al = [a[..., off[k - 1]: off[k]].reshape(-1, d ** k) for k in range(1, depth + 1)]
+    bl = [b[..., off[k - 1]: off[k]].reshape(-1, d ** k) for k in range(1, depth + 1)]
+
+    def product(xl, yl, bilinear_only=False):
+        out = []
+        for n in range(1, depth + 1):
+            acc = torch.zeros_like(xl[n - 1]) if bilinear_only else xl[n - 1] + yl[n - 1]
+            for k in range(1, n):
+                acc = acc + (xl[k - 1].unsqueeze(2) * yl[n - k - 1].unsqueeze(1)).reshape(acc.shape)
+            out.append(acc)
+        return out
+
+    out = torch.cat(product(al, bl), dim=1).reshape(lead + (off[-1],))
+
+    def grad_fn(g):
+        gl = [_cpu(g, torch.float64)[..., off[k - 1]: off[k]].reshape(-1, d ** k) for k in range(1, depth + 1)]
+        ga = [x.clone() for x in gl]
+        gb = [x.clone() for x in gl]
+        for n in range(1, depth + 1):
+            for k in range(1, n):
+                gn = gl[n - 1].reshape(-1, d ** k, d ** (n - k))
+                ga[k - 1] += (gn * bl[n - k - 1].unsqueeze(1)).sum(2)
+                gb[n - k - 1] += (gn * al[k - 1].unsqueeze(2)).sum(1)
+        return (torch.cat(ga, dim=1).reshape(lead + (off[-1],)), torch.cat(gb, dim=1).reshape(lead + (off[-1],)))
+
+    return out, grad_fn

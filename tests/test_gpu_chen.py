@@ -117,3 +117,18 @@ def test_argument_checks_and_opcheck(ps):
     g = torch.randn(2, D, device=DEV, dtype=torch.float64)
     torch.library.opcheck(torch.ops.pathsig_b200.chen_product_backward.default,
                           (a.detach(), b.detach(), g, depth, d), test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.parametrize("d,depth", [(2, 7), (4, 4), (8, 4), (6, 3)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-13), (torch.float32, 2e-6)])
+def test_matches_oracle_forward_and_backward(ps, oracle, d, depth, dtype, tol):
+    D = sum(d ** k for k in range(1, depth + 1))
+    a = util.normal_like((2, 3, D), 5) * 0.4
+    b = util.normal_like((2, 3, D), 6) * 0.4
+    g = util.normal_like((2, 3, D), 7)
+    want, grad_fn = oracle.chen_product(a.to(dtype).double(), b.to(dtype).double(), d, depth)
+    want_ga, want_gb = grad_fn(g.to(dtype).double())
+    got = ps.ops.chen_product(a.to(dtype).to(DEV), b.to(dtype).to(DEV), depth, d)
+    got_ga, got_gb = ps.ops.chen_product_backward(a.to(dtype).to(DEV), b.to(dtype).to(DEV), g.to(dtype).to(DEV), depth, d)
+    assert util.rel_error(got, want) < tol
+    assert util.rel_error(got_ga, want_ga) < tol and util.rel_error(got_gb, want_gb) < tol

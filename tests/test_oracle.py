@@ -16,6 +16,7 @@ import torch
 from pathsig_b200.projections import projections
 
 from . import tensor_algebra as ta
+from . import util
 
 
 def _path(B, L, d, seed=0, dtype=torch.float64):
@@ -193,3 +194,22 @@ def test_shuffle_identity(oracle):
     for i in range(d):
         for j in range(d):
             assert abs(s[i] * s[j] - s[d + i * d + j] - s[d + j * d + i]) < 1e-14
+
+
+@pytest.mark.parametrize("d,depth", [(2, 5), (3, 4), (5, 3)])
+def test_chen_product_glues_signatures(oracle, d, depth):
+    """S(x[:m+1]) (x) S(x[m:]) = S(x), and the gradient through the glued pieces equals the gradient
+    through the whole path (both sides computed by the oracle)."""
+    x = util.brownian_path(2, 14, d, seed=d + depth)
+    m = 6
+    whole = oracle.sig_forward(x, depth)
+    sa, sb = oracle.sig_forward(x[:, : m + 1].contiguous(), depth), oracle.sig_forward(x[:, m:].contiguous(), depth)
+    glued, grad_fn = oracle.chen_product(sa, sb, d, depth)
+    assert util.rel_error(glued, whole) < 1e-13
+    g = util.normal_like(whole.shape, 3)
+    ga, gb = grad_fn(g)
+    want = oracle.sig_backward(x, whole, g, depth)
+    got = torch.zeros_like(x)
+    got[:, : m + 1] += oracle.sig_backward(x[:, : m + 1].contiguous(), sa, ga, depth)
+    got[:, m:] += oracle.sig_backward(x[:, m:].contiguous(), sb, gb, depth)
+    assert util.rel_error(got, want) < 1e-12
