@@ -147,7 +147,9 @@ int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *c
  *   return PSIG_ERR_TOO_LARGE and must use psig_sig_backward.
  *   Every device that loads the library holds those 8 MiB until the process exits.
  *   The first call on each device looks up the array's device address (with that device
- *   current); make that first call before starting any stream capture.
+ *   current) and may make the CUDA runtime load the library's kernels onto the device; make it
+ *   once as a warm-up, before starting any stream capture and before the phase in which
+ *   allocations are forbidden.
  *   All calls on a device share the one array: the needed part is cleared on the stream before
  *   each use, and two calls whose GPU work overlaps (different streams, or different threads)
  *   would corrupt each other -- issue them on one stream or order them with events. */

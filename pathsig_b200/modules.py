@@ -55,6 +55,28 @@ def _no_words() -> torch.Tensor:
     return torch.empty(0, dtype=torch.int64, device=_default_device())
 
 
+def _host_codes(projection, words: torch.Tensor) -> List[int]:
+    codes = getattr(projection, "_host_codes", None)
+    return list(codes) if codes is not None else words.tolist()
+
+
+def _check_codes(codes: List[int], level_sizes: List[int], d: int, depth: int) -> None:
+    """Every stored code of an incomplete degree k must be a word of that degree: 0 <= code < d**k.
+    The kernels index dense images of a degree by these codes, so a bad code (a hand-made projection,
+    a state_dict from another configuration) would read or write out of bounds on the device."""
+    used = 0
+    for k in range(1, depth + 1):
+        size, full = int(level_sizes[k]), d ** k
+        if size == full:
+            continue
+        level = codes[used: used + size]
+        if len(level) < size:
+            raise ValueError(f"encoded_words holds {len(codes)} codes, fewer than level_sizes requires.")
+        if level and (min(level) < 0 or max(level) >= full):
+            raise ValueError(f"encoded_words has a code outside [0, {d}**{k}) at degree {k}.")
+        used += size
+
+
 class Signature(nn.Module):
     """Truncated signature of a batch of paths ``(B, L, d)`` -> ``(B, D)`` or ``(B, W, D)``."""
 
@@ -68,10 +90,24 @@ class Signature(nn.Module):
         self.register_buffer("_encoded_words", words if self.alternative_projection else _no_words(),
                              persistent=self.alternative_projection)
         self._level_sizes: List[int] = projection.level_sizes if self.alternative_projection else []
+        if self.alternative_projection:
+            _check_codes(_host_codes(projection, words), self._level_sizes, int(projection.path_dim), self.depth)
+            self.register_load_state_dict_post_hook(_recheck_loaded_words)
 
     def forward(self, path: torch.Tensor) -> torch.Tensor:
         return compute_signature(path, self.depth, self.alternative_projection, self._encoded_words,
                                  self._level_sizes, self.use_windows, self._windows)
+
+
+def _recheck_loaded_words(module, incompatible_keys) -> None:
+    """After load_state_dict: the word codes now in the buffers must still be words of this projection."""
+    _check_codes(module._encoded_words.tolist(), module._level_sizes, int(module.projection.path_dim), module.depth)
+    if isinstance(module, LogSignature):
+        top = module._top_words.tolist()
+        full = int(module.projection.path_dim) ** module.depth
+        if top and (min(top) < 0 or max(top) >= full):
+            raise ValueError("_top_words has a code outside the top degree.")
+        module._refresh_columns()
 
 
 class _SelectColumns(torch.autograd.Function):
@@ -121,10 +157,22 @@ class LogSignature(nn.Module):
                                  if self._level_sizes[k] != d ** k)
         self.register_buffer("_top_words", words[explicit_below_top:], persistent=True)
         self._ext_level_sizes = [0] + [d ** k for k in range(1, self.depth)] + [int(self._level_sizes[self.depth])]
-        columns = projection.logsig_indices().to(device=words.device, dtype=torch.int64).contiguous()
+        _check_codes(_host_codes(projection, words), self._level_sizes, d, self.depth)
+        host_columns = projection.logsig_indices().tolist()
+        columns = torch.tensor(host_columns, dtype=torch.int64, device=words.device)
         self.register_buffer("_indices_from_sig", columns, persistent=True)
+        self._refresh_columns(host_columns)
+        self.register_load_state_dict_post_hook(_recheck_loaded_words)
+
+    def _refresh_columns(self, host_columns: Optional[List[int]] = None) -> None:
+        """Facts derived from the column index actually in the buffer (re-derived after load_state_dict)."""
+        if host_columns is None:
+            host_columns = self._indices_from_sig.tolist()
+        width = sum(self._ext_level_sizes)
+        if host_columns and (min(host_columns) < 0 or max(host_columns) >= width):
+            raise ValueError(f"_indices_from_sig has a column outside [0, {width}).")
         # a projection that lists a word twice selects a column twice: those gradients must add up
-        self._columns_repeat = bool(torch.unique(columns).numel() != columns.numel())
+        self._columns_repeat = len(set(host_columns)) != len(host_columns)
 
     def forward(self, path: torch.Tensor) -> torch.Tensor:
         if self.alternative_projection:

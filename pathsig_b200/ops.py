@@ -74,6 +74,16 @@ def _ptr(t: Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr() if t.numel() > 0 else 0)
 
 
+def _check_same_device(anchor: Tensor, **operands: Tensor) -> None:
+    """Every tensor operand must live on the device the kernels are launched on (the anchor's).  The
+    dispatcher does not check this for operators registered from Python, and a pointer into another
+    GPU's memory would fault there (or be read silently over a peer mapping)."""
+    for name, t in operands.items():
+        if t.device != anchor.device:
+            raise RuntimeError(f"{name} must be on the same device as the path/signature "
+                               f"({name} is on {t.device}, expected {anchor.device})")
+
+
 def _check_words_cuda(encoded_words: Tensor) -> None:
     if not encoded_words.is_cuda:
         raise RuntimeError("encoded_words must be CUDA")
@@ -106,6 +116,7 @@ def _sig_desc(path: Tensor, depth: int, alt: bool, encoded_words: Tensor, level_
     desc.algo = _algo
     if alt:
         _check_words_cuda(encoded_words)
+        _check_same_device(path, encoded_words=encoded_words)
         if len(level_sizes) < depth + 1:
             raise RuntimeError("level_sizes must cover at least depth + 1 entries")
         need = 0
@@ -125,6 +136,7 @@ def _sig_desc(path: Tensor, depth: int, alt: bool, encoded_words: Tensor, level_
             raise RuntimeError("windows must be [W,2]")
         if windows.dtype not in (torch.int32, torch.int64):
             raise RuntimeError("windows must be int32")
+        _check_same_device(path, windows=windows)
         win = windows.to(torch.int32).contiguous()
         keep.append(win)
         desc.W = win.size(0)
@@ -151,6 +163,7 @@ def _log_desc(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: T
     if alt:
         if not fake:
             _check_words_cuda(encoded_words)
+            _check_same_device(signature, encoded_words=encoded_words)
         if len(level_sizes) < depth + 1:
             raise RuntimeError("level_sizes must have entries up to depth")
         desc.top_size = int(level_sizes[depth])
@@ -204,6 +217,7 @@ def _signature_backward_cuda(path_in, signature_in, grad_signature_in, depth, al
         raise RuntimeError("grad_signature must have same dtype as path")
     if signature_in.shape != grad_signature_in.shape:
         raise RuntimeError("grad_signature must match signature shape")
+    _check_same_device(path_in, signature=signature_in, grad_signature=grad_signature_in)
     path = path_in.contiguous()
     sig = signature_in.contiguous()
     grad = grad_signature_in.contiguous()
@@ -264,6 +278,7 @@ def _logsig_backward_cuda(signature_in, P_in, grad_logsig_in, depth, alternative
         raise RuntimeError("grad_logsig must have same dtype as sig")
     if grad_logsig_in.shape != signature_in.shape:
         raise RuntimeError("grad_logsig must match sig shape")
+    _check_same_device(signature_in, P=P_in, grad_logsig=grad_logsig_in)
     if len(level_sizes) <= int(depth):
         raise RuntimeError("level_sizes must have entries up to depth")
     d = int(level_sizes[1])  # the channel count travels in level_sizes[1], as in the reference
@@ -301,6 +316,7 @@ def _chen_desc(sig_a: Tensor, sig_b: Tensor, depth: int, d: int) -> _load.ChenDe
         raise RuntimeError("d must be >= 1")
     if sig_a.dtype != sig_b.dtype:
         raise RuntimeError("signatures must have the same dtype")
+    _check_same_device(sig_a, sig_b=sig_b)
     if sig_a.shape != sig_b.shape or sig_a.dim() < 1:
         raise RuntimeError("signatures must have the same shape (..., D)")
     D = sum(d ** k for k in range(1, depth + 1))
@@ -333,6 +349,7 @@ def _chen_product_backward_cuda(sig_a, sig_b, grad_out, depth, d):
         raise RuntimeError("grad_out must be CUDA")
     if grad_out.dtype != sig_a.dtype or grad_out.shape != sig_a.shape:
         raise RuntimeError("grad_out must match the signatures in dtype and shape")
+    _check_same_device(sig_a, grad_out=grad_out)
     a, b, g = sig_a.contiguous(), sig_b.contiguous(), grad_out.contiguous()
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     if ga.numel() == 0:

@@ -102,6 +102,7 @@ class Projection:
 
     def _finish(self, codes: List[int], sizes: List[int], device) -> None:
         self._level_sizes = sizes
+        self._host_codes = list(codes)  # host copy: consumers validate and index without a device read
         self._codes = torch.tensor(codes, dtype=torch.int64, device=device or _default_device())
 
     def logsig_indices(self) -> torch.Tensor:
@@ -111,7 +112,7 @@ class Projection:
         this returns, for every kept word, its column in that layout.
         """
         d = self.path_dim
-        codes = self._codes.tolist()
+        codes = self._host_codes if hasattr(self, "_host_codes") else self._codes.tolist()
         columns: List[int] = []
         dense_offset, used = 0, 0
         for n in range(1, self.depth):

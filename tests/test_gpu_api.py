@@ -288,3 +288,55 @@ def test_batches_beyond_grid_limits(ps, d, depth, B, L, dtype, log):
     assert torch.isfinite(out).all() and torch.isfinite(xg.grad).all()
     assert util.rel_error(out[rows], sub) < tol
     assert util.rel_error(xg.grad[rows], xs.grad) < tol
+
+
+def test_bad_word_codes_and_foreign_devices_raise_on_the_host(ps):
+    """Codes outside their degree and operands on another device are refused before any launch."""
+    proj = ps.projections.words([(0, 1), (2, 2), (1, 0, 2)], 3, 3, full_levels=(1,), device=DEV)
+    proj._host_codes[1] = 9          # not a word of degree 2 over 3 letters
+    proj._codes[1] = 9
+    with pytest.raises(ValueError, match="outside"):
+        ps.Signature(depth=3, projection=proj)
+    with pytest.raises(ValueError, match="outside"):
+        ps.LogSignature(depth=3, projection=proj)
+    good = ps.projections.words([(0, 1), (2, 2), (1, 0, 2)], 3, 3, full_levels=(1,), device=DEV)
+    mod = ps.Signature(depth=3, projection=good)
+    bad_state = {k: v.clone() for k, v in mod.state_dict().items()}
+    bad_state["_encoded_words"][2] = 27
+    with pytest.raises(ValueError, match="outside"):
+        mod.load_state_dict(bad_state)
+    # a CPU tensor among CUDA operands: refused by the operator itself
+    x = _path(2, 8, 3)
+    with pytest.raises(RuntimeError, match="same device|must be CUDA"):
+        ps.ops.compute_signature(x, 3, True, good.encoded_words.cpu(), good.level_sizes, False,
+                                 torch.empty((0, 2), dtype=torch.int32, device=DEV))
+    if torch.cuda.device_count() > 1:
+        other = good.encoded_words.to("cuda:1")
+        with pytest.raises(RuntimeError, match="same device"):
+            ps.ops.compute_signature(x, 3, True, other, good.level_sizes, False,
+                                     torch.empty((0, 2), dtype=torch.int32, device=DEV))
+
+
+def test_loaded_column_index_with_repeats_keeps_every_gradient(ps):
+    """A state_dict may replace the column index by one that selects a column twice; the gradients of
+    both selections must add up (the scatter used for repeat-free indices would drop one)."""
+    proj = ps.projections.lyndon(3, 3, device=DEV)
+    mod = ps.LogSignature(depth=3, projection=proj)
+    assert mod._columns_repeat is False
+    state = {k: v.clone() for k, v in mod.state_dict().items()}
+    state["_indices_from_sig"][1] = state["_indices_from_sig"][0]
+    mod.load_state_dict(state)
+    assert mod._columns_repeat is True
+    x = _path(2, 12, 3).requires_grad_(True)
+    out = mod(x)
+    g = torch.randn_like(out)
+    (out * g).sum().backward()
+    full = ps.LogSignature(depth=3)
+    x2 = x.detach().clone().requires_grad_(True)
+    sel = full(x2)
+    # columns of the hybrid layout == columns of the dense log-signature below the top degree
+    idx = state["_indices_from_sig"]
+    dense_cols = _full_columns(proj)
+    hybrid_to_dense = torch.cat([torch.arange(3 + 9, device=DEV), dense_cols[3 + 3:]])  # degrees 1, 2 dense; top listed
+    (sel.index_select(-1, hybrid_to_dense[idx]) * g).sum().backward()
+    torch.testing.assert_close(x.grad, x2.grad, atol=1e-10, rtol=1e-10)

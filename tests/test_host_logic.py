@@ -192,3 +192,30 @@ def test_install_as_pathsig_aliases_the_package():
     import pathsig
     assert pathsig.Signature is ps.Signature and pathsig.projections is ps.projections
     assert torch.ops.pathsig.compute_signature is not None
+
+
+def test_operands_on_another_device_are_refused_before_any_launch():
+    """A tensor operand on a different device than the path must raise on the host: the dispatcher
+    does not check devices for operators registered from Python, and the kernels would otherwise
+    receive a pointer into another GPU's memory."""
+    from pathsig_b200 import ops
+    path = torch.empty(2, 4, 3, device="meta")
+    other = torch.empty(5, dtype=torch.int64)  # lives on the CPU: a different device
+    with pytest.raises(RuntimeError, match="encoded_words must be on the same device"):
+        ops._check_same_device(path, encoded_words=other)
+    ops._check_same_device(path, windows=torch.empty((0, 2), dtype=torch.int32, device="meta"))
+
+
+def test_word_codes_are_range_checked_on_the_host():
+    from pathsig_b200 import modules
+    # d = 3, depth 3: degree 1 complete, two words at degree 2, one at degree 3
+    modules._check_codes([0, 8, 26], [0, 3, 2, 1], 3, 3)
+    with pytest.raises(ValueError, match=r"outside \[0, 3\*\*2\)"):
+        modules._check_codes([0, 9, 26], [0, 3, 2, 1], 3, 3)
+    with pytest.raises(ValueError, match=r"outside \[0, 3\*\*3\)"):
+        modules._check_codes([0, 8, 27], [0, 3, 2, 1], 3, 3)
+    with pytest.raises(ValueError, match="fewer than level_sizes requires"):
+        modules._check_codes([0, 8], [0, 3, 2, 1], 3, 3)
+    # the projections keep a host copy of their codes, so module construction reads nothing back
+    proj = ps.projections.words([(0, 1), (2, 2), (1, 0, 2)], 3, 3, full_levels=(1,), device="cpu")
+    assert proj._host_codes == proj.encoded_words.tolist() == [1, 8, 11]

@@ -77,6 +77,20 @@ def test_static_scratch_entry_point_matches_regular_one(dtype, windowed):
     assert util.rel_error(first, want) < tol
     assert util.rel_error(second, want) < tol
 
+    # The reason the entry point exists: a call takes no device memory.  After the warm calls above
+    # (the first one may load the kernels' module) the free memory of the device and the bytes held
+    # by torch's allocator are the same before and after one more call.
+    third = torch.full_like(x, float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    held_before = torch.cuda.memory_allocated()
+    assert lib.psig_sig_backward_static(ctypes.byref(desc), _ptr(x), _ptr(sig), _ptr(g), _ptr(third), stream) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after >= free_before  # nothing was taken from the device
+    assert torch.cuda.memory_allocated() == held_before
+    assert util.rel_error(third, want) < tol
+
 
 def test_static_scratch_entry_point_refuses_oversized_problems():
     from pathsig_b200 import _load
