@@ -1,19 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the signature hot path: paths*steps/s for forward+backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5] [--impl ours|reference]
 
 One "step" is one forward + backward pass of the hot path over one batch of seeded synthetic
-Brownian paths.  The default workload (``cfg2``) is the windowed depth-4 signature of
-(256, 1024, 8) float32 paths over 61 sliding windows [16k, 16k+64); under ``torchrun`` every
-rank processes its own batch of that size (weak scaling, no collective on the data path).
+Brownian paths.  The default workload (``cfg5``) is the depth-4 signature of (4096, 2048, 16)
+float32 paths, the largest configuration of the baseline specification that fits one GPU; under
+``torchrun`` the 4096 paths are sharded over the ranks (strong scaling, no collective on the
+data path).  Every other workload keeps its batch per rank (weak scaling).
 
 The JSON line printed by rank 0 carries: ``value`` (device-timed, inputs resident in HBM),
 ``e2e`` (same metric through ``pathsig_b200.Signature`` with pinned-host inputs, H2D and D2H
 copies inside the timed region), ``roofline`` (FP32 FMA bound kernels: algorithmic FLOP of the
 backward operator over its measured duration, against an FFMA peak measured in the same
-process), ``roofline_hbm``, ``cpu_baseline`` (the CPU oracle on a bounded sample), ``clocks``
-and ``others`` (the remaining workloads of the baseline specification, short runs).
+process), ``roofline_hbm``, ``cpu_baseline`` (the CPU oracle on a bounded, fixed sample),
+``clocks``, ``gather`` (at N > 1: the optional all-gather of the sharded output, timed apart from
+the step) and ``others`` (the remaining workloads of the baseline specification: median of
+several repeats, each with the reference's CUDA operators, the parity of this library against
+them on the same tensors, and the CPU oracle on a fixed sample).
 
 ``--impl reference`` times the CPU restatement of the reference algorithm (``oracle/``) on the
 host cores instead; the reference itself has no CPU implementation.
@@ -21,6 +25,7 @@ host cores instead; the reference itself has no CPU implementation.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import math
 import os
@@ -38,18 +43,22 @@ import torch  # noqa: E402
 
 METRIC = "paths*steps/s, forward+backward"
 UNIT = "paths*steps/s"
+HEADLINE = "cfg5"
 
-# DRAM traffic of one launch of the dominant kernel, from ncu captures summarised under
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
-NCU_TRAFFIC_BYTES = {
-    # sig_backward_tiled at (8,4): 180.6 MB captured at B=128 (profiles/sig_backward_tiled_d8_n4_cfg2_b128.md),
-    # proportional in units -> B=256
-    "cfg2": 361.3e6,
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of a workload's dominant
+# kernel as captured with ncu on a reduced batch; it grows in proportion to the batch, so the bench
+# line scales it by (paths of the timed launch / paths of the capture) and says so.
+NCU_TRAFFIC = {
+    "cfg5": {"kernel": "sig_backward_tiled (d=16, depth 4)", "captured_paths": None, "dram_bytes": None},
+    "cfg2": {"kernel": "sig_backward_tiled (d=8, depth 4)", "captured_paths": 128, "dram_bytes": 180.6e6},
 }
+
+# Fixed CPU samples (paths of each workload the CPU oracle runs); work is linear in the batch.
+CPU_SAMPLE_PATHS = {"cfg1": 32, "cfg2": 16, "cfg3": 64, "cfg4": 64, "cfg5": 4}
 
 
 # ----------------------------------------------------------------------------------------------
-# workloads (BASELINE.json configs 1-5)
+# workloads (the five configurations of the baseline specification)
 # ----------------------------------------------------------------------------------------------
 
 def _brownian(B, L, d, seed):
@@ -160,6 +169,12 @@ class Workload:
             return sum(self.d ** k for k in range(1, self.depth + 1))
         return mod.projection.sig_size
 
+    def degree_widths(self):
+        """Columns per degree of the module's output (for the per-degree parity metric)."""
+        if self.spec["kind"] == "sig":
+            return [self.d ** k for k in range(1, self.depth + 1)]
+        return [int(s) for s in self.mod.projection.level_sizes[1: self.depth + 1]]
+
     def flop_fwd_bwd(self):
         return 8.0 * self.fma_fwd * self.units  # forward F FMAs, backward credited 3F
 
@@ -197,7 +212,7 @@ class Workload:
 
     def step_fwd_bwd(self, events=None):
         """Forward + backward with dL/dout = G (the loss is sum(out * G)).  For the signature
-        modules the two operators are called directly; returns grad wrt the path."""
+        modules the two operators are called directly; returns (output, grad wrt the path)."""
         import pathsig_b200 as ps
         m = self.mod
         if isinstance(m, ps.Signature):
@@ -209,7 +224,7 @@ class Workload:
                                            m._encoded_words, m._level_sizes, m.use_windows, m._windows)
             if events is not None:
                 events[1].record()
-            return gp
+            return sig, gp
         x = self.x.detach().requires_grad_(True)
         out = m(x)
         if events is not None:
@@ -217,14 +232,17 @@ class Workload:
         out.backward(self.G)
         if events is not None:
             events[1].record()
-        return x.grad
+        return out.detach(), x.grad
 
     def kernels_per_step(self):
-        import pathsig_b200 as ps
-        if isinstance(self.mod, ps.Signature):
-            generic = self.spec["kind"] != "sig"  # generic backward adds the increments->points kernel
-            return 1 + 1 + (1 if generic else 0)
-        return 1 + 1 + 1 + 1 + 1  # sig fwd, log fwd, log bwd, sig bwd, increments->points
+        """Kernels of this library launched by one forward + backward step (counted, not assumed)."""
+        from pathsig_b200 import _load
+        lib = _load.ensure_loaded()
+        torch.cuda.synchronize()
+        before = lib.psig_kernel_launches()
+        self.step_fwd_bwd()
+        torch.cuda.synchronize()
+        return int(lib.psig_kernel_launches() - before)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -291,6 +309,9 @@ def _dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch.distributed as dist
+        # plain NCCL rings/trees over NVLink: the optional gather is the only collective, and it need
+        # not bind this process's memory to an NVLink multicast object
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
@@ -328,11 +349,27 @@ def time_steps(fn, steps, warmup, world, device):
     return _max_over_ranks(start.elapsed_time(end), world, device)
 
 
+def time_repeats(fn, steps, warmup, repeats, world, device):
+    """ms per step of `repeats` timed loops of `steps` calls each: (median, min, max)."""
+    per_step = []
+    for r in range(repeats):
+        per_step.append(time_steps(fn, steps, warmup if r == 0 else 1, world, device) / steps)
+    return statistics.median(per_step), min(per_step), max(per_step)
+
+
+def _probe_lib():
+    """The measurement-only probe library built from bench_probe.cu (FP32 FMA peak loops)."""
+    lib = ctypes.CDLL(os.path.join(ROOT, "libbench_probe.so"))
+    for name in ("psig_probe_fp32_fma", "psig_probe_fp32_fma_packed"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int64
+        fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    return lib
+
+
 def measure_fp32_peak(device, packed=False):
     """TFLOP/s of a register-only FFMA loop (psig_probe_fp32_fma[_packed]), best of 5."""
-    import ctypes
-    from pathsig_b200 import _load
-    lib = _load.ensure_loaded()
+    lib = _probe_lib()
     probe = lib.psig_probe_fp32_fma_packed if packed else lib.psig_probe_fp32_fma
     scratch = torch.zeros(16, device=device)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -349,13 +386,14 @@ def measure_fp32_peak(device, packed=False):
     return best
 
 
-def cpu_baseline(name, threads=None, seconds_hint=15.0):
-    """The CPU oracle (a port of the reference algorithm) on a bounded sample of the workload."""
+def cpu_baseline(name, threads=None):
+    """The CPU oracle (a port of the reference algorithm) on a fixed sample of the workload:
+    one forward + backward of CPU_SAMPLE_PATHS[name] paths.  Returns (record, seconds)."""
     from oracle import oracle
     cores = threads or os.cpu_count() or 1
     oracle.set_threads(cores)
     spec = SPECS[name]
-    B = min(spec["B"], 2 * cores if name != "cfg5" else cores)
+    B = min(spec["B"], CPU_SAMPLE_PATHS[name])
     wl = Workload(name, B=B)
     x = wl.host_path()
     win = wl.windows
@@ -380,14 +418,35 @@ def cpu_baseline(name, threads=None, seconds_hint=15.0):
         g = _normal(sig.shape, 1)
         oracle.sig_backward(x, sig, g, wl.depth, ew, ls, win)
     dt = time.perf_counter() - t0
-    return {"value": wl.units / dt, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{name} with B={B} of {spec['B']} paths, float32, one forward+backward, {dt:.2f} s wall "
-                      f"(work is linear in B); port of the reference per-word algorithm, OpenMP over paths"}, dt
+    return {"value": wl.units / dt, "unit": UNIT, "cores": cores, "kind": "port", "sample_paths": B,
+            "sample": f"{name} with B={B} of {spec['B']} paths (fixed sample), float32, one forward+backward, "
+                      f"{dt:.2f} s wall (work is linear in B); port of the reference per-word algorithm, "
+                      f"OpenMP over paths"}, dt
+
+
+def _parity(ours_out, ours_grad, ref_out, ref_grad, widths):
+    """Both parity metrics of this library against the reference's CUDA operators on the same tensors:
+    whole tensor max|a-b| / max(1, max|b|) and per degree max|a-b| / max|b| for the output; for the
+    input gradient max|a-b| / max|b| over the whole (B, L, d) tensor."""
+    def maxabs(t):
+        return float(t.abs().max().item()) if t.numel() else 0.0
+
+    whole = maxabs(ours_out - ref_out) / max(1.0, maxabs(ref_out))
+    per, off = [], 0
+    for w in widths:
+        if w:
+            den = maxabs(ref_out[..., off: off + w]) or 1.0
+            per.append(maxabs(ours_out[..., off: off + w] - ref_out[..., off: off + w]) / den)
+        off += w
+    return {"output_whole": whole, "output_per_degree": per,
+            "input_gradient": maxabs(ours_grad - ref_grad) / (maxabs(ref_grad) or 1.0),
+            "against": "the reference's CUDA operators, same tensors, float32"}
 
 
 def reference_cuda_baseline(wl, device, steps=5, warmup=2):
     """The reference's own CUDA operators (built unchanged into oracle/_ref/ by oracle/build_ref.py)
-    on the same tensors, as a reported baseline.  Returns None when that library is not there."""
+    on the same tensors, as a reported baseline, plus the parity of this library against their
+    results (outside every timed region).  Returns None when that library is not there."""
     lib = os.path.join(ROOT, "oracle", "_ref", "libpathsig_ops.so")
     if not os.path.isfile(lib):
         return None
@@ -407,10 +466,10 @@ def reference_cuda_baseline(wl, device, steps=5, warmup=2):
                 return sig, logsig, cache, logsig.index_select(-1, idx)
 
             def fwd_bwd():
-                sig, logsig, cache, _ = fwd()
+                sig, logsig, cache, out = fwd()
                 g_full = torch.zeros_like(logsig).index_add_(-1, idx, wl.G)
                 g_sig = ref.logsig_backward(sig, cache, g_full, *largs)
-                return ref.signature_backward(wl.x, sig, g_sig, *sargs)
+                return out, ref.signature_backward(wl.x, sig, g_sig, *sargs)
         else:
             args = (m.depth, m.alternative_projection, m._encoded_words, list(m._level_sizes), m.use_windows, m._windows)
 
@@ -419,13 +478,18 @@ def reference_cuda_baseline(wl, device, steps=5, warmup=2):
 
             def fwd_bwd():
                 sig = ref.compute_signature(wl.x, *args)
-                return ref.signature_backward(wl.x, sig, wl.G, *args)
+                return sig, ref.signature_backward(wl.x, sig, wl.G, *args)
 
         ms_f = time_steps(fwd, steps, warmup, 1, device)
         ms_fb = time_steps(fwd_bwd, steps, warmup, 1, device)
+        ref_out, ref_grad = fwd_bwd()
+        our_out, our_grad = wl.step_fwd_bwd()
+        torch.cuda.synchronize()
+        parity = _parity(our_out, our_grad, ref_out, ref_grad, wl.degree_widths())
+        del ref_out, ref_grad, our_out, our_grad
         return {"fwd": {"value": wl.units * steps / (ms_f * 1e-3), "ms_per_step": ms_f / steps},
                 "fwd_bwd": {"value": wl.units * steps / (ms_fb * 1e-3), "ms_per_step": ms_fb / steps},
-                "unit": UNIT, "steps": steps,
+                "unit": UNIT, "steps": steps, "parity": parity,
                 "what": "reference CUDA operators compiled for sm_100 from its unchanged sources, same tensors, "
                         "device-timed; a reported baseline, not part of the product"}
     except Exception as exc:  # the baseline must never break the benchmark
@@ -437,7 +501,6 @@ def reference_cuda_baseline(wl, device, steps=5, warmup=2):
 # ----------------------------------------------------------------------------------------------
 
 def run_reference(args):
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -450,15 +513,17 @@ def run_reference(args):
         last, _dt = cpu_baseline(name)
     total = time.perf_counter() - t0
     spec = SPECS[name]
-    B = min(spec["B"], 2 * last["cores"] if name != "cfg5" else last["cores"])
+    B = last["sample_paths"]
     units = Workload(name, B=B).units
     value = units * args.steps / total
     last["value"] = value
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{name}: {spec['desc']}; CPU sample B={B}", "timing": "host wall clock"},
+        "higher_is_better": True, "scaling": "strong" if name == HEADLINE else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{name}: {spec['desc']}; fixed CPU sample of B={B} paths per step "
+                               f"(throughput is linear in B)", "timing": "host wall clock"},
         "cpu_baseline": last,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -468,40 +533,54 @@ def run_reference(args):
     emit(line)
 
 
-def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e2e=False, fp32_peak=None):
-    import pathsig_b200 as ps
+def _steps_for(fn, target_s, lo, hi):
+    """Number of calls of fn that take about target_s seconds (one synchronised probe of 3 calls)."""
+    fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    per = max((time.perf_counter() - t0) / 3, 1e-6)
+    return int(max(lo, min(hi, target_s / per)))
+
+
+def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e2e=False, fp32_peak=None,
+                     repeats=1, auto_steps=False):
     wl = Workload(name, B=per_rank_B, seed=int(os.environ.get("RANK", "0"))).build(device)
     res = {"workload": name}
+    if auto_steps:
+        # sub-millisecond workloads: each of the `repeats` timed loops runs for about 0.2 s
+        steps = _steps_for(lambda: wl.step_fwd_bwd(), 0.2, steps, 20000)
+        if world > 1:
+            steps = int(_max_over_ranks(float(steps), world, device))
     # forward only
-    ms_f = time_steps(wl.step_forward, steps, warmup, world, device)
-    # forward + backward, with the backward operator bracketed by events
+    f_med, f_min, f_max = time_repeats(wl.step_forward, steps, warmup, repeats, world, device)
+    # forward + backward, with the backward operator bracketed by events in the first loop
     pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     it = iter(pairs)
 
     def step():
         wl.step_fwd_bwd(next(it, None))
 
-    for _ in range(warmup):
-        wl.step_fwd_bwd()
-    _barrier(world)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        step()
-    end.record()
-    _barrier(world)
-    ms_fb = _max_over_ranks(start.elapsed_time(end), world, device)
+    per_step = []
+    for r in range(repeats):
+        per_step.append(time_steps(step if r == 0 else wl.step_fwd_bwd, steps, warmup if r == 0 else 1, world,
+                                   device) / steps)
+    fb_med, fb_min, fb_max = statistics.median(per_step), min(per_step), max(per_step)
     bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
     total_units = wl.units * world
     res.update({
         "units_per_step": total_units,
         "fma_per_unit_fwd": wl.fma_fwd,
-        "fwd": {"value": total_units * steps / (ms_f * 1e-3), "ms_per_step": ms_f / steps},
-        "fwd_bwd": {"value": total_units * steps / (ms_fb * 1e-3), "ms_per_step": ms_fb / steps},
+        "steps": steps, "repeats": repeats,
+        "fwd": {"value": total_units / (f_med * 1e-3), "ms_per_step": f_med, "ms_min": f_min, "ms_max": f_max},
+        "fwd_bwd": {"value": total_units / (fb_med * 1e-3), "ms_per_step": fb_med, "ms_min": fb_min, "ms_max": fb_max,
+                    "timed_s": sum(per_step) * steps * 1e-3},
         "bwd_op_ms": bwd_ms,
-        "tflops_fwd": wl.flop_fwd() * world / (ms_f / steps * 1e-3) / 1e12,
-        "tflops_fwd_bwd": wl.flop_fwd_bwd() * world / (ms_fb / steps * 1e-3) / 1e12,
-        "hbm_gbs_fwd_bwd": wl.bytes_fwd_bwd * world / (ms_fb / steps * 1e-3) / 1e9,
+        "tflops_fwd": wl.flop_fwd() * world / (f_med * 1e-3) / 1e12,
+        "tflops_fwd_bwd": wl.flop_fwd_bwd() * world / (fb_med * 1e-3) / 1e12,
+        "hbm_gbs_fwd_bwd": wl.bytes_fwd_bwd * world / (fb_med * 1e-3) / 1e9,
         "kernels_per_step": wl.kernels_per_step(),
     })
     if wl.units < 200000:
@@ -517,8 +596,9 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 wl.step_fwd_bwd()
-            ms_g = time_steps(graph.replay, steps, warmup, world, device)
-            res["fwd_bwd_cuda_graph"] = {"value": total_units * steps / (ms_g * 1e-3), "ms_per_step": ms_g / steps}
+            g_med, g_min, g_max = time_repeats(graph.replay, steps, warmup, repeats, world, device)
+            res["fwd_bwd_cuda_graph"] = {"value": total_units / (g_med * 1e-3), "ms_per_step": g_med,
+                                         "ms_min": g_min, "ms_max": g_max}
             del graph
         except Exception as exc:  # reported, never fatal
             res["fwd_bwd_cuda_graph"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:160]}
@@ -592,7 +672,29 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
                       "api": "pathsig_b200.Signature(...)(x); torch.dot(out.flatten(), G.flatten()).backward(); every step copies its batch "
                              "from pinned host memory and its grad and loss back, on a copy stream overlapped with "
                              "the neighbouring steps' compute (one extra batch is staged ahead)"}
+        del xd, gd, xh, gh
     return res
+
+
+def measure_gather(wl, world, device, steps=5, warmup=2):
+    """The optional gathered output: all ranks' (B/N, D) signatures concatenated on every rank by one
+    NCCL all-gather (pathsig_b200.distributed.gather_batch).  Timed on the device apart from the step,
+    max over ranks.  Bytes per rank = what a rank receives from its peers."""
+    from pathsig_b200.distributed import gather_batch
+    out, _ = wl.step_fwd_bwd()
+    sizes = [out.shape[0]] * world
+
+    def fn():
+        return gather_batch(out, sizes=sizes)
+
+    ms = time_steps(fn, steps, warmup, world, device) / steps
+    full = fn()
+    ok = bool(full.shape[0] == out.shape[0] * world)
+    received = out.numel() * out.element_size() * (world - 1)
+    del full
+    return {"ms": ms, "bytes_received_per_rank": received, "gbs_per_rank": received / (ms * 1e-3) / 1e9,
+            "gathered_shape_ok": ok, "collective": "NCCL all_gather_into_tensor over NVLink (NVLS off), device-timed, "
+                                                   "max over ranks; not part of the step"}
 
 
 def run_ours(args):
@@ -621,77 +723,102 @@ def run_ours(args):
     hbm_peak, hbm_src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
 
     name = args.workload
+    strong = name == HEADLINE  # the headline's batch is sharded over the ranks; the others keep theirs per rank
+    per_rank_B = args.batch
+    if strong and per_rank_B is None:
+        per_rank_B = SPECS[name]["B"] // world
     sampler = ClockSampler(local if world > 1 else 0)
     if rank == 0:
         sampler.start()
     t_begin = time.perf_counter()
-    main = measure_workload(name, args.steps, args.warmup, world, device, per_rank_B=args.batch, with_e2e=True,
-                            fp32_peak=fp32_peak)
-    # keep the same step running long enough for the 100 ms clock sampler to see it under load
+    short = Workload(name, B=per_rank_B).units < 2_000_000
+    main = measure_workload(name, args.steps, args.warmup, world, device, per_rank_B=per_rank_B, with_e2e=True,
+                            fp32_peak=fp32_peak, repeats=5 if short else 1)
     wl = main["_wl"]
+    # a short workload keeps running until the 100 ms clock sampler has seen it under load
     while time.perf_counter() - t_begin < 2.0:
         for _ in range(20):
             wl.step_fwd_bwd()
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     if clocks is not None:
-        clocks["sampled_over"] = "timed regions plus continuation of the same step up to 2 s"
+        clocks["sampled_over"] = "the timed regions of the headline workload"
+
+    gather = None
+    if world > 1 and SPECS[name]["kind"] == "sig" and "windows" not in SPECS[name]:
+        gather = measure_gather(wl, world, device)
+
+    cpu = None
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, _ = cpu_baseline(name)
+        few = wl.units > 2_000_000  # the reference runs for seconds on the large workloads
+        ref_cuda = reference_cuda_baseline(wl, device, steps=1 if few else 5, warmup=1 if few else 2)
+    main.pop("_wl")
+    kernels_per_step = main["kernels_per_step"]
+    bwd_flop = wl.flop_bwd()
+    bytes_fwd_bwd = wl.bytes_fwd_bwd
+    paths_per_launch = wl.B
+    del wl
+    torch.cuda.empty_cache()
 
     others = {}
     if not args.no_others:
         for other in SPECS:
             if other == name:
                 continue
-            B = None
-            if other == "cfg5":
-                B = SPECS["cfg5"]["B"] // world  # strong scaling: the 4096 paths are sharded over the ranks
-            # short runs: 3 warm-up steps, then 20 timed steps of the sub-millisecond workloads, 5 of config 5
-            n_other = max(3, min(args.steps, 5 if other == "cfg5" else 20))
-            r = measure_workload(other, n_other, 3, world, device, per_rank_B=B, fp32_peak=fp32_peak)
+            big = Workload(other).units > 2_000_000
+            B = SPECS[other]["B"] // world if other == HEADLINE else None
+            r = measure_workload(other, 5 if big else 20, 3, world, device, per_rank_B=B, fp32_peak=fp32_peak,
+                                 repeats=1 if big else 5, auto_steps=not big)
             other_wl = r.pop("_wl")
             if rank == 0 and world == 1 and not args.no_cpu:
-                # the reference's CUDA operators on the same tensors (one timed step of config 5: it runs for seconds)
-                few = other == "cfg5"
-                r["reference_cuda"] = reference_cuda_baseline(other_wl, device, steps=1 if few else 5,
-                                                              warmup=1 if few else 2)
+                r["reference_cuda"] = reference_cuda_baseline(other_wl, device, steps=1 if big else 5,
+                                                              warmup=1 if big else 2)
+                r["cpu_baseline"] = cpu_baseline(other)[0]
             del other_wl
-            if other == "cfg5":
-                r["scaling"] = "strong"
+            r["scaling"] = "strong" if other == HEADLINE else "weak"
             others[other] = r
             torch.cuda.empty_cache()
 
-    cpu = None
-    ref_cuda = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu, _ = cpu_baseline(name)
-        ref_cuda = reference_cuda_baseline(wl, device)
-
     if rank != 0:
         return
-    main.pop("_wl")
     spec = SPECS[name]
     steps = args.steps
-    bwd_flop = wl.flop_bwd()
     achieved = bwd_flop / (main["bwd_op_ms"] * 1e-3) / 1e12
+    traffic = None
+    traffic_note = "no ncu capture of this workload's dominant kernel"
+    cap = NCU_TRAFFIC.get(name)
+    if cap and cap["dram_bytes"]:
+        scale = paths_per_launch / cap["captured_paths"]
+        traffic = cap["dram_bytes"] * scale
+        traffic_note = (f"ncu capture of {cap['kernel']} at {cap['captured_paths']} paths: {cap['dram_bytes']:.4g} B "
+                        f"of dram read+write per launch, scaled x{scale:g} to the {paths_per_launch} paths of a timed "
+                        f"launch (traffic grows in proportion to the batch)")
     line = {
         "metric": METRIC, "value": main["fwd_bwd"]["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": main["fwd_bwd"]["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{name}: {spec['desc']}", "per_gpu_batch": wl.B, "global_batch": wl.B * world,
+        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{name}: {spec['desc']}", "per_gpu_batch": paths_per_launch,
+                   "global_batch": paths_per_launch * world,
                    "units_per_step": main["units_per_step"], "l2": "inputs_larger_than_l2"
-                   if wl.bytes_fwd_bwd > 126e6 else "inputs smaller than L2 (latency-bound configuration)",
+                   if bytes_fwd_bwd > 126e6 else "inputs smaller than L2 (latency-bound configuration)",
                    "parallelism": f"batch shards x{world}, no collective"},
         "forward_only": main["fwd"],
+        "timed": {"repeats": main["repeats"], "ms_min": main["fwd_bwd"]["ms_min"], "ms_max": main["fwd_bwd"]["ms_max"],
+                  "timed_s": main["fwd_bwd"]["timed_s"]},
         "clocks": clocks,
         "e2e": main["e2e"],
-        "gpu_launches": steps * main["kernels_per_step"],
+        "gpu_launches": steps * kernels_per_step,
         "roofline": {
-            "bound": "fp32_fma", "kernel": "signature_backward operator (cudaMemsetAsync of grad_path + sig_backward_tiled)",
+            "bound": "fp32_fma", "kernel": "signature_backward operator (sig_backward_tiled, preceded by the "
+                                           "cudaMemsetAsync of grad_path where blocks share points)",
             "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
-            "peak_source": "register-only FMA loops (psig_probe_fp32_fma / _packed) measured in this process, best of the two; MEASURED_PEAKS.json has no FP32 figure",
+            "peak_source": "register-only FMA loops (psig_probe_fp32_fma / _packed) measured in this process, best of "
+                           "the two; MEASURED_PEAKS.json has no FP32 figure",
             "peak_scalar_fma": fp32_peak_scalar, "peak_packed_fma": fp32_peak_packed,
             "flop_per_launch": bwd_flop, "flop_convention": "backward credited 3 x F_fwd FMAs per path*step",
-            "traffic": NCU_TRAFFIC_BYTES.get(name),
+            "traffic": traffic, "traffic_source": traffic_note,
             "whole_step": {"achieved": main["tflops_fwd_bwd"], "frac": main["tflops_fwd_bwd"] / (fp32_peak * world)},
         },
         "roofline_hbm": {"bound": "hbm", "achieved": main["hbm_gbs_fwd_bwd"], "peak": hbm_peak * world if hbm_peak else None,
@@ -699,6 +826,7 @@ def run_ours(args):
                          "peak_source": hbm_src, "bytes": "read path + write signature + read grad + write grad_path"},
         "cpu_baseline": cpu,
         "reference_cuda": ref_cuda,
+        "gather": gather,
         "others": others,
     }
     emit(line)
@@ -724,12 +852,12 @@ def main():
     _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg2", choices=sorted(SPECS))
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(SPECS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the short runs of the other workloads")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU and reference-CUDA baseline legs")
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch of the workload")
     ap.add_argument("--profile", action="store_true",
                     help="only run warmup+steps forward+backward passes of the workload (for ncu captures)")

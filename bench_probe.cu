@@ -1,6 +1,15 @@
-// Measurement aid: a register-only FP32 FMA loop used by bench.py to measure the FFMA peak of
-// the device it runs on (the roofline denominator of the signature kernels).
-#include "common.cuh"
+// Measurement aid of bench.py, not part of the product library: register-only FP32 FMA loops that
+// give the FFMA peak of the device they run on (the roofline denominator of the signature kernels).
+// Built by __graft_entry__.build() into libbench_probe.so beside bench.py.
+//
+//   int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream)
+//   int64_t psig_probe_fp32_fma_packed(...)   the same loop as packed two-lane FMAs (fma.rn.f32x2)
+//
+// Each launches `blocks` x 256 threads that run `iters` x 128 dependent-chain-free FMAs on registers
+// only and returns the number of FMAs issued (negative on a bad argument or a failed launch); the
+// caller times the launch.  `scratch` must point to at least 4 bytes of device memory.
+#include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace psig {
 namespace {
@@ -48,18 +57,18 @@ __global__ void __launch_bounds__(256) ffma2_probe(float *out, int iters, float 
 
 extern "C" int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream)
 {
-    if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
+    if (blocks <= 0 || iters <= 0 || !scratch) return -4;
     psig::ffma_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
                                                                           0.999999f, 1e-7f);
-    if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    if (cudaGetLastError() != cudaSuccess) return -7;
     return (int64_t)blocks * 256 * (int64_t)iters * 8 * 16;  // FMAs issued
 }
 
 extern "C" int64_t psig_probe_fp32_fma_packed(int blocks, int iters, void *scratch, void *stream)
 {
-    if (blocks <= 0 || iters <= 0 || !scratch) return PSIG_ERR_SHAPE;
+    if (blocks <= 0 || iters <= 0 || !scratch) return -4;
     psig::ffma2_probe<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float *>(scratch), iters,
                                                                            0.999999f, 1e-7f);
-    if (psig::check_launch() != PSIG_OK) return PSIG_ERR_CUDA;
+    if (cudaGetLastError() != cudaSuccess) return -7;
     return (int64_t)blocks * 256 * (int64_t)iters * 8 * 16;  // FMAs issued (two per packed instruction)
 }

@@ -95,6 +95,10 @@ typedef struct PsigLogDesc {
 } PsigLogDesc;
 
 int psig_abi_version(void);
+/* Diagnostic with no counterpart in the reference: kernels this library has launched in this process
+ * so far (all entry points, all threads).  A caller that wants to know how many kernels a step costs
+ * reads it before and after the step. */
+int64_t psig_kernel_launches(void);
 const char *psig_status_string(int status);
 
 /* Width D of one signature row for this description, or a negative PsigStatus. */
@@ -178,14 +182,6 @@ int psig_chen_forward(const PsigChenDesc *desc, const void *a, const void *b, vo
  * uses no atomics: results are bit-reproducible from run to run. */
 int psig_chen_backward(const PsigChenDesc *desc, const void *a, const void *b, const void *grad_out,
                        void *grad_a, void *grad_b, void *stream);
-
-/* Measurement aid with no counterpart in the reference: launches `blocks` x 256 threads that each
- * run `iters` x 128 dependent-chain-free FP32 FMAs on registers only, and returns the number of
- * FMAs issued (or a negative PsigStatus).  Timed by the caller, it gives the FP32 FMA peak used
- * as the roofline denominator.  `scratch` must point to at least 4 bytes of device memory. */
-int64_t psig_probe_fp32_fma(int blocks, int iters, void *scratch, void *stream);
-/* The same loop issued as packed two-lane FMAs (fma.rn.f32x2); same FMA count returned. */
-int64_t psig_probe_fp32_fma_packed(int blocks, int iters, void *scratch, void *stream);
 
 #ifdef __cplusplus
 }

@@ -5,18 +5,26 @@ strongest parity pin there is: the GPU tests load this library next to ours (its
 live in ``torch.ops.pathsig``, ours in ``torch.ops.pathsig_b200``) and compare outputs on the
 same tensors, and ``tests/golden/make_golden.py`` records its outputs as fixtures.
 
-The sources are compiled where they lie (the checkout named by ``$PATHSIG_REFERENCE_ROOT``, or
-the default location of ``reference_root()``) with plain nvcc commands; the reference's own CMake build is not run and
-no source file is copied.  Outputs go to ``oracle/_ref/`` only, which git ignores.  When the
-reference tree is absent (for example on a GPU box) the function leaves an existing library
+The sources are compiled where they lie (the checkout named by the ``root`` argument or by
+``$PATHSIG_REFERENCE_ROOT``) with plain nvcc commands; the reference's own CMake build is not run and
+no source file enters the repository.  Outputs go to ``oracle/_ref/`` only, which git ignores.  When no
+reference tree is given or found (for example on a GPU box) the function leaves an existing library
 alone and reports whether one is there.
+
+The same step stages the two acceptance files of the reference's test-suite that need nothing but the
+public ``pathsig`` API (``tests/test_windows.py``, ``tests/test_projections.py``), byte for byte, under
+``oracle/_ref/reference_tests/`` with their SHA-256 in ``PROVENANCE.txt``, so that the GPU tests can run
+them unmodified against this package (``tests/test_gpu_reference_suites.py``).
 """
 from __future__ import annotations
 
+import hashlib
 import os
+import shutil
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
+from typing import Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
@@ -30,16 +38,40 @@ SOURCES = [
 ]
 
 
-def reference_root() -> str:
-    return os.environ.get("PATHSIG_REFERENCE_ROOT", "/root/reference")
+TESTS_DIR = os.path.join(OUT_DIR, "reference_tests")
+ACCEPTANCE_TESTS = ["tests/test_windows.py", "tests/test_projections.py"]
 
 
-def build(force: bool = False, verbose: bool = False) -> bool:
+def reference_root(root: Optional[str] = None) -> Optional[str]:
+    """The reference checkout to build from: the argument, else ``$PATHSIG_REFERENCE_ROOT``, else none."""
+    return root or os.environ.get("PATHSIG_REFERENCE_ROOT") or None
+
+
+def stage_acceptance_tests(root: str) -> None:
+    """Copy the reference's API-only test files, unmodified, next to the built library."""
+    files = [os.path.join(root, t) for t in ACCEPTANCE_TESTS]
+    if not all(os.path.isfile(f) for f in files):
+        return
+    os.makedirs(TESTS_DIR, exist_ok=True)
+    lines = ["Unmodified copies of files of the reference's test-suite (tobiasny12/pathsig v0.1.7), staged by",
+             "oracle/build_ref.py for tests/test_gpu_reference_suites.py.  sha256  path-in-the-reference", ""]
+    for rel, src in zip(ACCEPTANCE_TESTS, files):
+        shutil.copyfile(src, os.path.join(TESTS_DIR, os.path.basename(rel)))
+        with open(src, "rb") as fh:
+            lines.append(f"{hashlib.sha256(fh.read()).hexdigest()}  {rel}")
+    with open(os.path.join(TESTS_DIR, "PROVENANCE.txt"), "w") as fh:
+        fh.write("\n".join(lines) + "\n")
+
+
+def build(force: bool = False, verbose: bool = False, root: Optional[str] = None) -> bool:
     """Returns True when ``oracle/_ref/libpathsig_ops.so`` exists afterwards."""
-    root = reference_root()
+    root = reference_root(root)
+    if root is None:
+        return os.path.isfile(LIB)
     srcs = [os.path.join(root, s) for s in SOURCES]
     if not all(os.path.isfile(s) for s in srcs):
         return os.path.isfile(LIB)
+    stage_acceptance_tests(root)
     if os.path.isfile(LIB) and not force:
         newest = max(os.path.getmtime(s) for s in srcs)
         if os.path.getmtime(LIB) >= newest:
@@ -86,5 +118,6 @@ def build(force: bool = False, verbose: bool = False) -> bool:
 
 
 if __name__ == "__main__":
-    ok = build(force="--force" in sys.argv, verbose=True)
+    positional = [a for a in sys.argv[1:] if not a.startswith("--")]
+    ok = build(force="--force" in sys.argv, verbose=True, root=positional[0] if positional else None)
     print("reference library:", LIB if ok else "unavailable")

@@ -12,8 +12,7 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libpathsig_b200.so"
-# PATHSIG_B200_LIB selects another build of the same library (kernel tuning experiments).
-LIB_PATH = os.environ.get("PATHSIG_B200_LIB") or os.path.join(_HERE, LIB_NAME)
+LIB_PATH = os.path.join(_HERE, LIB_NAME)
 MAX_DEPTH = 12
 ABI_VERSION = 1
 
@@ -81,8 +80,7 @@ EXPORTS = {
     "psig_logsig_forward": (_int, [_LogP, _vp, _vp, _vp, _vp]),
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
-    "psig_probe_fp32_fma": (_i64, [_int, _int, _vp, _vp]),
-    "psig_probe_fp32_fma_packed": (_i64, [_int, _int, _vp, _vp]),
+    "psig_kernel_launches": (_i64, []),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),
     "psig_sig_backward_static_limit": (_i64, []),
     "psig_chen_size": (_i64, [_ChenP]),

@@ -2,7 +2,14 @@
 // Declarations and the reference operators they stand in for: include/pathsig_b200.h.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace psig {
+
+namespace {
+std::atomic<long long> g_kernel_launches{0};
+}
+void count_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int make_level_table(int d, int depth, bool projected, const int64_t *level_sizes, const int64_t *words,
                      bool top_only, LevelTable *out)
@@ -91,6 +98,8 @@ using namespace psig;
 extern "C" {
 
 int psig_abi_version(void) { return PSIG_ABI_VERSION; }
+
+int64_t psig_kernel_launches(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 const char *psig_status_string(int status)
 {

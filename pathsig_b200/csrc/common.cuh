@@ -68,6 +68,13 @@ template <typename T>
 int tiled_sig_backward(const PsigSigDesc &desc, const T *path, const T *sig, const T *grad, T *grad_path,
                        void *workspace, cudaStream_t stream);
 
-inline int check_launch() { return cudaGetLastError() == cudaSuccess ? PSIG_OK : PSIG_ERR_CUDA; }
+// Called once after every kernel launch: counts the launch (psig_kernel_launches) and reports a
+// failed one.
+void count_launch();
+inline int check_launch()
+{
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PSIG_OK : PSIG_ERR_CUDA;
+}
 
 }  // namespace psig

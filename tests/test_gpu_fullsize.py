@@ -21,12 +21,14 @@ from . import util
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 TOL = 1e-5
-# Input gradients at full length, float32 against a float64 oracle: both this library and the
-# reference roll the prefix signatures back over hundreds of steps in float32, which leaves
-# 3e-6 .. 1e-5 of the largest gradient entry depending on the row (measured), so the bound for
-# these long float32 sweeps is looser than for the signature itself.  (The reference's own
-# float32 gradient tolerances are 1e-4 and 1e-3: tests/test_sig.py:26-34, tests/test_logsig.py:24-31.)
-GRAD_TOL = 3e-5
+# Input gradients against the float64 oracle.  Measured over full batches: 4e-7 .. 1.5e-6 of the
+# largest entry (worst single path 4e-6) for the four signature configurations, below the
+# reference's own float32 error on the same inputs (5e-7 .. 2.7e-6).
+GRAD_TOL = 1e-5
+# The float32 log-signature of config 4 loses digits to the cancellation inside the logarithm: this
+# library is 2.6e-5 from the float64 value at degree 6 and 1.2e-5 in the gradient, the reference
+# 3.8e-5 and 1.8e-5 (tests/test_gpu_reference_fullsize.py asserts the three-way comparison).
+LOG_F32_TOL = 5e-5
 
 
 @pytest.fixture(scope="module")
@@ -127,8 +129,10 @@ def test_config4_full(ps, oracle):
     want, want_grad = oracle.logsignature(wl.x[rows].double().cpu(), 6, top_words=mod._top_words.cpu(),
                                           ext_level_sizes=mod._ext_level_sizes, indices=mod._indices_from_sig.cpu(),
                                           grad_out=wl.G[rows].double().cpu())
-    assert util.rel_error(out[rows], want) < TOL
-    assert util.rel_error(grad[rows], want_grad) < GRAD_TOL
+    widths = util.level_widths(4, 6, mod.projection.level_sizes)
+    per_degree = util.level_rel_errors(out[rows], want, widths)
+    assert max(per_degree[:4]) < TOL and max(per_degree) < LOG_F32_TOL, per_degree
+    assert util.rel_error(grad[rows], want_grad) < LOG_F32_TOL
 
 
 def test_config5_shard(ps, oracle):
@@ -146,9 +150,10 @@ def test_config5_shard(ps, oracle):
     s2 = out[:8, 16:272].double().reshape(8, 16, 16)
     chen = a[:, 16:272].reshape(8, 16, 16) + b[:, 16:272].reshape(8, 16, 16) + a[:, :16, None] * b[:, None, :16]
     assert (s2 - chen).abs().max().item() < TOL * s2.abs().max().item()
-    # two paths against the oracle, forward; one path backward
-    x64 = wl.x[:2].double().cpu()
+    # eight paths spread over the shard against the oracle, forward and backward
+    rows = [0, 1, 77, 200, 301, 400, 510, 511]
+    x64 = wl.x[rows].double().cpu()
     want = oracle.sig_forward(x64, 4)
-    assert max(util.level_rel_errors(out[:2], want, util.level_widths(16, 4))) < TOL
-    want_grad = oracle.sig_backward(x64[:1], want[:1], wl.G[:1].double().cpu(), 4)
-    assert util.rel_error(grad[:1], want_grad) < GRAD_TOL
+    assert max(util.level_rel_errors(out[rows], want, util.level_widths(16, 4))) < TOL
+    want_grad = oracle.sig_backward(x64, want, wl.G[rows].double().cpu(), 4)
+    assert util.rel_error(grad[rows], want_grad) < GRAD_TOL
