@@ -40,7 +40,7 @@ extern "C" {
 #endif
 
 #define PSIG_MAX_DEPTH 12
-#define PSIG_ABI_VERSION 1
+#define PSIG_ABI_VERSION 2
 
 typedef enum PsigStatus {
     PSIG_OK = 0,
@@ -59,9 +59,12 @@ typedef enum PsigDtype { PSIG_F32 = 0, PSIG_F64 = 1 } PsigDtype;
 
 /* Algorithm selection for psig_sig_forward / psig_sig_backward (desc.algo). */
 typedef enum PsigAlgo {
-    PSIG_ALGO_AUTO = 0,    /* register-tiled kernel when one exists for (dtype, d, depth), else generic */
+    PSIG_ALGO_AUTO = 0,    /* register-tiled kernel when one exists for (dtype, d, depth); the prefix-closure
+                              kernels for projected rows with enough work to repay their one-off
+                              specialisation; else generic */
     PSIG_ALGO_GENERIC = 1, /* always the generic per-prefix kernel */
-    PSIG_ALGO_TILED = 2    /* register-tiled kernel or PSIG_ERR_UNSUPPORTED */
+    PSIG_ALGO_TILED = 2,   /* register-tiled kernel or PSIG_ERR_UNSUPPORTED */
+    PSIG_ALGO_CLOSURE = 3  /* prefix-closure kernels specialised for the word set, or PSIG_ERR_UNSUPPORTED */
 } PsigAlgo;
 
 /* Problem description shared by the signature entry points. */
@@ -78,6 +81,9 @@ typedef struct PsigSigDesc {
     int64_t level_sizes[PSIG_MAX_DEPTH + 1];  /* host */
     int32_t algo;                             /* PsigAlgo */
     int32_t reserved;
+    const int64_t *words_host;                /* optional HOST copy of `words` (same layout).  The prefix-closure
+                                                 kernels are generated from the word set, which has to be readable
+                                                 on the host; NULL rules that family out for projected rows. */
 } PsigSigDesc;
 
 /* Problem description of the signature <-> log-signature entry points.  The signature is in
@@ -111,7 +117,8 @@ int64_t psig_logsig_size(const PsigLogDesc *desc);
 int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void *stream);
 
 /* Scratch bytes psig_sig_backward needs for this description: 0 for the register-tiled kernels,
- * sizeof(scalar)*B*(L-1)*d for the generic ones. */
+ * sizeof(scalar)*B*(L-1)*d for the generic and the prefix-closure ones.  May build the specialised
+ * kernels of a projected description on first use (seconds, once per word set and device). */
 int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
 
 /* grad_path (B, L, d) = d/dpath of sum(signature * grad_sig).  `sig` is the forward output for
@@ -140,6 +147,18 @@ int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
  * Replaces pathsig::logsig_backward (src/pathsig/backward/sig_backward_launch.cu:307-460). */
 int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,
                          void *grad_sig, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Prefix-closure kernels (no counterpart in the reference, whose threads each recompute the private
+ * prefix chain of one word, src/pathsig/forward/sig_kernels.cu:99-113): diagnostics of the code
+ * generator.  psig_closure_source writes the CUDA C++ generated for the row layout of `desc` (which must
+ * carry words_host for listed degrees) cut into about `target_bins` bins, NUL-terminated, into `buffer`
+ * (up to `capacity` bytes) and returns its full length, or a negative PsigStatus.  stats (5 entries, may
+ * be NULL): closure nodes, algorithmic forward FMAs per path*step, FMAs the generated forward code
+ * executes per path*step (bins recompute the ancestors of their first node), bins, node values per lane.
+ * psig_closure_compile compiles such a source with NVRTC for `arch` (e.g. "sm_100a") without touching a
+ * device; the compiler's log goes to `log`.  Neither call launches anything. */
+int64_t psig_closure_source(const PsigSigDesc *desc, int target_bins, char *buffer, int64_t capacity, int64_t *stats);
+int psig_closure_compile(const char *source, const char *arch, char *log, int64_t log_capacity);
 
 /* No counterpart in the reference.  Same result as psig_sig_backward computed by the generic
  * kernel, for callers that have no scratch memory to pass and may not allocate any: hosts whose

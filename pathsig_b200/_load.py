@@ -14,10 +14,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libpathsig_b200.so"
 LIB_PATH = os.path.join(_HERE, LIB_NAME)
 MAX_DEPTH = 12
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 PSIG_F32, PSIG_F64 = 0, 1
-ALGO_AUTO, ALGO_GENERIC, ALGO_TILED = 0, 1, 2
+ALGO_AUTO, ALGO_GENERIC, ALGO_TILED, ALGO_CLOSURE = 0, 1, 2, 3
 
 _lock = threading.Lock()
 _lib = None
@@ -38,6 +38,7 @@ class SigDesc(ctypes.Structure):
         ("level_sizes", ctypes.c_int64 * (MAX_DEPTH + 1)),
         ("algo", ctypes.c_int32),
         ("reserved", ctypes.c_int32),
+        ("words_host", ctypes.c_void_p),
     ]
 
 
@@ -81,6 +82,8 @@ EXPORTS = {
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "psig_kernel_launches": (_i64, []),
+    "psig_closure_source": (_i64, [_SigP, _int, ctypes.c_char_p, _i64, ctypes.POINTER(ctypes.c_int64)]),
+    "psig_closure_compile": (_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, _i64]),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),
     "psig_sig_backward_static_limit": (_i64, []),
     "psig_chen_size": (_i64, [_ChenP]),

@@ -79,13 +79,32 @@ int log_table(const PsigLogDesc *desc, LevelTable *lt)
     return make_level_table(desc->d, desc->depth, true, sizes, desc->top_words, true, lt);
 }
 
-bool use_tiled(const PsigSigDesc *desc, int *rc)
+enum class Family { kGeneric, kTiled, kClosure };
+
+// Kernel family for a description; the same function serves the forward call, the workspace query and
+// the backward call, so the three always agree.
+//   tiled:   dense rows (or dense below a listed top degree) of a shape with a register-tiled instance;
+//   closure: other projected rows whose word set is known on the host, when there is enough work to
+//            repay the one-off specialisation (where both exist the two measured within 6 % of each
+//            other on a (4, 6) row with a Lyndon top degree, so the family without a compilation wins);
+//   generic: everything else.
+Family select_family(const PsigSigDesc *desc, const LevelTable &lt, int *rc)
 {
     *rc = PSIG_OK;
-    const bool eligible = tiled_supported(*desc);
-    if (desc->algo == PSIG_ALGO_GENERIC) return false;
-    if (desc->algo == PSIG_ALGO_TILED && !eligible) { *rc = PSIG_ERR_UNSUPPORTED; return false; }
-    return eligible;
+    if (desc->algo == PSIG_ALGO_GENERIC) return Family::kGeneric;
+    if (desc->algo == PSIG_ALGO_CLOSURE) {
+        if (closure_supported(*desc, lt)) return Family::kClosure;
+        *rc = PSIG_ERR_UNSUPPORTED;
+        return Family::kGeneric;
+    }
+    const bool tiled = tiled_supported(*desc);
+    if (desc->algo == PSIG_ALGO_TILED) {
+        if (!tiled) *rc = PSIG_ERR_UNSUPPORTED;
+        return tiled ? Family::kTiled : Family::kGeneric;
+    }
+    if (tiled) return Family::kTiled;
+    if (closure_worthwhile(*desc, lt) && closure_supported(*desc, lt)) return Family::kClosure;
+    return Family::kGeneric;
 }
 
 size_t dtype_size(int dtype) { return dtype == PSIG_F32 ? 4 : 8; }
@@ -125,6 +144,24 @@ int64_t psig_sig_size(const PsigSigDesc *desc)
     return rc != PSIG_OK ? rc : lt.total;
 }
 
+int64_t psig_closure_source(const PsigSigDesc *desc, int target_bins, char *buffer, int64_t capacity, int64_t *stats)
+{
+    LevelTable lt;
+    const int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (target_bins < 1) return PSIG_ERR_SHAPE;
+    long long st[5] = {0, 0, 0, 0, 0};
+    const long long n = closure_source(*desc, lt, target_bins, buffer, capacity, st);
+    if (stats) for (int i = 0; i < 5; ++i) stats[i] = st[i];
+    return n;
+}
+
+int psig_closure_compile(const char *source, const char *arch, char *log, int64_t log_capacity)
+{
+    if (!source || !arch) return PSIG_ERR_NULL;
+    return closure_compile_only(source, arch, log, log_capacity);
+}
+
 int64_t psig_logsig_size(const PsigLogDesc *desc)
 {
     LevelTable lt;
@@ -140,12 +177,17 @@ int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void 
     if (desc->B == 0 || lt.total == 0) return PSIG_OK;
     if (!path || !out) return PSIG_ERR_NULL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool tiled = use_tiled(desc, &rc);
+    const Family family = select_family(desc, lt, &rc);
     if (rc != PSIG_OK) return rc;
-    if (tiled) {
+    if (family == Family::kTiled) {
         if (desc->dtype == PSIG_F32)
             return tiled_sig_forward<float>(*desc, static_cast<const float *>(path), static_cast<float *>(out), st);
         return tiled_sig_forward<double>(*desc, static_cast<const double *>(path), static_cast<double *>(out), st);
+    }
+    if (family == Family::kClosure) {
+        if (desc->dtype == PSIG_F32)
+            return closure_sig_forward<float>(*desc, lt, static_cast<const float *>(path), static_cast<float *>(out), st);
+        return closure_sig_forward<double>(*desc, lt, static_cast<const double *>(path), static_cast<double *>(out), st);
     }
     if (desc->dtype == PSIG_F32)
         return generic_sig_forward<float>(*desc, lt, static_cast<const float *>(path), static_cast<float *>(out), st);
@@ -157,9 +199,9 @@ int64_t psig_sig_backward_workspace(const PsigSigDesc *desc)
     LevelTable lt;
     int rc = sig_table(desc, &lt);
     if (rc != PSIG_OK) return rc;
-    const bool tiled = use_tiled(desc, &rc);
+    const Family family = select_family(desc, lt, &rc);
     if (rc != PSIG_OK) return rc;
-    if (tiled) return tiled_sig_backward_workspace(*desc);
+    if (family == Family::kTiled) return tiled_sig_backward_workspace(*desc);
     return (int64_t)dtype_size(desc->dtype) * desc->B * (desc->L - 1) * desc->d;
 }
 
@@ -176,9 +218,18 @@ int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig
     if (need < 0) return (int)need;
     if (need > 0 && (!workspace || workspace_bytes < need)) return PSIG_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool tiled = use_tiled(desc, &rc);
+    const Family family = select_family(desc, lt, &rc);
     if (rc != PSIG_OK) return rc;
-    if (tiled) {
+    if (family == Family::kClosure) {
+        if (desc->dtype == PSIG_F32)
+            return closure_sig_backward<float>(*desc, lt, static_cast<const float *>(path),
+                                               static_cast<const float *>(sig), static_cast<const float *>(grad_sig),
+                                               static_cast<float *>(grad_path), static_cast<float *>(workspace), st);
+        return closure_sig_backward<double>(*desc, lt, static_cast<const double *>(path),
+                                            static_cast<const double *>(sig), static_cast<const double *>(grad_sig),
+                                            static_cast<double *>(grad_path), static_cast<double *>(workspace), st);
+    }
+    if (family == Family::kTiled) {
         if (desc->dtype == PSIG_F32)
             return tiled_sig_backward<float>(*desc, static_cast<const float *>(path), static_cast<const float *>(sig),
                                              static_cast<const float *>(grad_sig), static_cast<float *>(grad_path),

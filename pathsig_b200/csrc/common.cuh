@@ -68,6 +68,19 @@ template <typename T>
 int tiled_sig_backward(const PsigSigDesc &desc, const T *path, const T *sig, const T *grad, T *grad_path,
                        void *workspace, cudaStream_t stream);
 
+// Prefix-closure kernels generated for the word set (closure_jit.cu).  `worthwhile` is a cheap test
+// of the description; `supported` builds (and caches) the plan, which compiles on first use.
+bool closure_worthwhile(const PsigSigDesc &desc, const LevelTable &lt);
+bool closure_supported(const PsigSigDesc &desc, const LevelTable &lt);
+template <typename T>
+int closure_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, T *out, cudaStream_t stream);
+template <typename T>
+int closure_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T *path, const T *sig, const T *grad,
+                         T *grad_path, T *inc_grad_ws, cudaStream_t stream);
+long long closure_source(const PsigSigDesc &desc, const LevelTable &lt, int target_bins, char *buffer, long long capacity,
+                         long long *stats);
+int closure_compile_only(const char *text, const char *arch, char *log, long long log_capacity);
+
 // Called once after every kernel launch: counts the launch (psig_kernel_launches) and reports a
 // failed one.
 void count_launch();

@@ -15,8 +15,9 @@ another namespace (``pathsig_b200.install_as_pathsig`` uses it for ``pathsig``).
 """
 from __future__ import annotations
 
+import collections
 import ctypes
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 from torch import Tensor
@@ -49,9 +50,33 @@ _algo = _load.ALGO_AUTO
 
 
 def set_algorithm(name: str) -> None:
-    """Select the signature kernel family: "auto", "generic" or "tiled"."""
+    """Select the signature kernel family: "auto", "generic", "tiled" or "closure"."""
     global _algo
-    _algo = {"auto": _load.ALGO_AUTO, "generic": _load.ALGO_GENERIC, "tiled": _load.ALGO_TILED}[name]
+    _algo = {"auto": _load.ALGO_AUTO, "generic": _load.ALGO_GENERIC, "tiled": _load.ALGO_TILED,
+             "closure": _load.ALGO_CLOSURE}[name]
+
+
+# Host copies of word-code tensors.  The prefix-closure kernels are generated from the word set, so the
+# library wants the codes in host memory; reading them back on every call would synchronise, so the
+# copy is made once per (storage, version) and kept while the device tensor is alive.  An entry holds a
+# reference to its device tensor, which keeps the address from being reused by another tensor.
+_HOST_WORDS_LIMIT = 64
+_host_words_cache: "collections.OrderedDict" = collections.OrderedDict()
+
+
+def _host_words(words: Tensor) -> Optional[Tensor]:
+    key = (words.data_ptr(), words._version, words.numel(), words.device.index)
+    hit = _host_words_cache.get(key)
+    if hit is not None:
+        _host_words_cache.move_to_end(key)
+        return hit[1]
+    if torch.cuda.is_current_stream_capturing():
+        return None  # no device read inside a graph capture; the library then uses another kernel family
+    host = words.detach().cpu().contiguous()
+    _host_words_cache[key] = (words, host)
+    while len(_host_words_cache) > _HOST_WORDS_LIMIT:
+        _host_words_cache.popitem(last=False)
+    return host
 
 
 # --------------------------------------------------------------------------------------
@@ -129,6 +154,11 @@ def _sig_desc(path: Tensor, depth: int, alt: bool, encoded_words: Tensor, level_
             raise RuntimeError("encoded_words holds fewer codes than level_sizes requires")
         desc.words = encoded_words.data_ptr() if encoded_words.numel() > 0 else None
         keep.append(encoded_words)
+        if encoded_words.numel() > 0:
+            host = _host_words(encoded_words)
+            if host is not None:
+                desc.words_host = host.data_ptr()
+                keep.append(host)
     if use_windows:
         if not windows.is_cuda:
             raise RuntimeError("windows must be CUDA")

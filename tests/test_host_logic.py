@@ -219,3 +219,49 @@ def test_word_codes_are_range_checked_on_the_host():
     # the projections keep a host copy of their codes, so module construction reads nothing back
     proj = ps.projections.words([(0, 1), (2, 2), (1, 0, 2)], 3, 3, full_levels=(1,), device="cpu")
     assert proj._host_codes == proj.encoded_words.tolist() == [1, 8, 11]
+
+
+def _closure_desc(codes, level_sizes, d, depth):
+    from pathsig_b200 import _load
+    desc = _load.SigDesc()
+    desc.dtype, desc.d, desc.depth, desc.B, desc.L, desc.projected = _load.PSIG_F32, d, depth, 64, 16, 1
+    for k in range(1, depth + 1):
+        desc.level_sizes[k] = level_sizes[k]
+    host = torch.tensor(codes, dtype=torch.int64)
+    desc.words_host = host.data_ptr()
+    desc.words = host.data_ptr()  # only offsets of it are formed on the host
+    return desc, host
+
+
+def test_closure_generator_counts_and_compiles_for_sm100a():
+    """The code generator of the prefix-closure kernels: its closure of the config-3 word set has the
+    algorithmic FMA count the benchmark credits, and the generated CUDA compiles for sm_100a with NVRTC
+    (no device needed)."""
+    import ctypes
+
+    import bench
+    from pathsig_b200 import _load
+    lib = _load.ensure_loaded()
+    wl = bench.Workload("cfg3")
+    proj = ps.projections.words([w for w in wl.words if len(w) > 1], 6, 8, full_levels=(1,), device="cpu")
+    desc, keep = _closure_desc(proj.encoded_words.tolist(), proj.level_sizes, 8, 6)
+    stats = (ctypes.c_int64 * 5)()
+    n = lib.psig_closure_source(ctypes.byref(desc), 16, None, 0, stats)
+    assert n > 0
+    nodes, algorithmic, executed, bins, per_lane = list(stats)
+    assert algorithmic == wl.fma_fwd            # one FMA per (closure node, target degree) pair
+    assert algorithmic <= executed <= 2 * algorithmic
+    assert 1 <= bins <= 16 and per_lane <= 64 and nodes >= 208
+    # a small word set, compiled
+    small = ps.projections.words([(0, 1), (2, 2), (1, 0, 2), (1, 0, 0)], 3, 3, full_levels=(1,), device="cpu")
+    desc, keep = _closure_desc(small.encoded_words.tolist(), small.level_sizes, 3, 3)
+    n = lib.psig_closure_source(ctypes.byref(desc), 2, None, 0, stats)
+    buf = ctypes.create_string_buffer(n + 1)
+    assert lib.psig_closure_source(ctypes.byref(desc), 2, buf, n + 1, stats) == n
+    assert b"closure_forward" in buf.value and b"closure_backward" in buf.value
+    log = ctypes.create_string_buffer(1 << 14)
+    rc = lib.psig_closure_compile(buf.value, b"sm_100a", log, 1 << 14)
+    assert rc == 0, log.value.decode()
+    # a word listed twice has no unique column: the plan is refused
+    desc, keep = _closure_desc([1, 1], [0, 3, 2, 0], 3, 3)
+    assert lib.psig_closure_source(ctypes.byref(desc), 2, None, 0, stats) < 0
