@@ -54,7 +54,7 @@ NCU_TRAFFIC = {
 }
 
 # Fixed CPU samples (paths of each workload the CPU oracle runs); work is linear in the batch.
-CPU_SAMPLE_PATHS = {"cfg1": 32, "cfg2": 16, "cfg3": 64, "cfg4": 64, "cfg5": 4}
+CPU_SAMPLE_PATHS = {"cfg1": 32, "cfg2": 16, "cfg3": 64, "cfg4": 64, "cfg5": 8}
 
 
 # ----------------------------------------------------------------------------------------------

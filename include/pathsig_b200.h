@@ -98,6 +98,14 @@ typedef struct PsigLogDesc {
     int64_t rows;               /* B or B*W */
     int64_t top_size;           /* words kept at degree `depth` */
     const int64_t *top_words;   /* device codes of the top degree, or NULL when it is dense */
+    /* Projected log-signature (row-in-shared-memory kernels only): the logarithm and the column selection
+     * that follows it in the reference (src/pathsig/modules.py:134-135) as ONE kernel.  lower_columns
+     * lists, in output order, the positions (in a dense row of the degrees below `depth`) of the words
+     * kept below the top degree; the output row is those n_lower_columns values followed by the whole top
+     * degree, and psig_logsig_backward takes the gradient in that same projected layout.  NULL / 0: every
+     * position is kept (the layout of pathsig::sig_to_logsig). */
+    const int64_t *lower_columns;   /* device, or NULL */
+    int64_t n_lower_columns;
 } PsigLogDesc;
 
 int psig_abi_version(void);
@@ -105,12 +113,22 @@ int psig_abi_version(void);
  * so far (all entry points, all threads).  A caller that wants to know how many kernels a step costs
  * reads it before and after the step. */
 int64_t psig_kernel_launches(void);
+/* Diagnostics of the bulk-copy (TMA) staging of the register-tiled forward kernel; no counterpart in the
+ * reference.  A block waits for a staged chunk of points for a bounded number of polls; when the wait
+ * runs out it reads the same bytes with plain loads (same result) and counts the event.
+ * psig_bulk_copy_timeouts returns the count on the current device since the last call and clears it;
+ * psig_set_bulk_wait_polls sets the bound on the current device (<= 0: the default, 2^20 polls) so that
+ * a test can make the wait run out.  Both synchronise the device; neither belongs in a hot loop. */
+int64_t psig_bulk_copy_timeouts(void);
+int psig_set_bulk_wait_polls(int polls);
 const char *psig_status_string(int status);
 
 /* Width D of one signature row for this description, or a negative PsigStatus. */
 int64_t psig_sig_size(const PsigSigDesc *desc);
-/* Width of one row in the hybrid layout of a PsigLogDesc, or a negative PsigStatus. */
+/* Width of one signature row in the hybrid layout of a PsigLogDesc, or a negative PsigStatus. */
 int64_t psig_logsig_size(const PsigLogDesc *desc);
+/* Width of one log-signature row: psig_logsig_size, or n_lower_columns + top_size when lower_columns is set. */
+int64_t psig_logsig_out_size(const PsigLogDesc *desc);
 
 /* out[(b*max(W,1)+w)*D + i] = signature coordinate i of path b over window w.
  * Replaces pathsig::compute_signature (src/pathsig/forward/sig_launch.cu:75-225). */

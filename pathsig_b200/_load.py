@@ -52,6 +52,8 @@ class LogDesc(ctypes.Structure):
         ("rows", ctypes.c_int64),
         ("top_size", ctypes.c_int64),
         ("top_words", ctypes.c_void_p),
+        ("lower_columns", ctypes.c_void_p),
+        ("n_lower_columns", ctypes.c_int64),
     ]
 
 
@@ -74,6 +76,7 @@ EXPORTS = {
     "psig_status_string": (ctypes.c_char_p, [_int]),
     "psig_sig_size": (_i64, [_SigP]),
     "psig_logsig_size": (_i64, [_LogP]),
+    "psig_logsig_out_size": (_i64, [_LogP]),
     "psig_sig_forward": (_int, [_SigP, _vp, _vp, _vp]),
     "psig_sig_backward_workspace": (_i64, [_SigP]),
     "psig_sig_backward": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
@@ -82,6 +85,8 @@ EXPORTS = {
     "psig_logsig_backward_workspace": (_i64, [_LogP]),
     "psig_logsig_backward": (_int, [_LogP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "psig_kernel_launches": (_i64, []),
+    "psig_bulk_copy_timeouts": (_i64, []),
+    "psig_set_bulk_wait_polls": (_int, [_int]),
     "psig_closure_source": (_i64, [_SigP, _int, ctypes.c_char_p, _i64, ctypes.POINTER(ctypes.c_int64)]),
     "psig_closure_compile": (_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, _i64]),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),

@@ -3,6 +3,9 @@
 #include "common.cuh"
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 namespace psig {
 
@@ -10,6 +13,24 @@ namespace {
 std::atomic<long long> g_kernel_launches{0};
 }
 void count_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool prepare_kernel_once(const void *kernel, size_t dynamic_smem, bool prefer_shared_carveout)
+{
+    static std::mutex mutex;
+    static std::map<std::pair<const void *, int>, size_t> granted;  // (kernel, device) -> shared memory + 1
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return false;
+    std::lock_guard<std::mutex> lock(mutex);
+    size_t &have = granted[std::make_pair(kernel, device)];
+    if (have > dynamic_smem) return true;
+    if (dynamic_smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic_smem) != cudaSuccess)
+        return false;
+    if (prefer_shared_carveout && have == 0)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    have = dynamic_smem + 1;
+    return true;
+}
 
 int make_level_table(int d, int depth, bool projected, const int64_t *level_sizes, const int64_t *words,
                      bool top_only, LevelTable *out)
@@ -120,6 +141,10 @@ int psig_abi_version(void) { return PSIG_ABI_VERSION; }
 
 int64_t psig_kernel_launches(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
+int64_t psig_bulk_copy_timeouts(void) { return tiled_bulk_copy_timeouts(); }
+
+int psig_set_bulk_wait_polls(int polls) { return tiled_set_bulk_wait_polls(polls); }
+
 const char *psig_status_string(int status)
 {
     switch (status) {
@@ -167,6 +192,16 @@ int64_t psig_logsig_size(const PsigLogDesc *desc)
     LevelTable lt;
     const int rc = log_table(desc, &lt);
     return rc != PSIG_OK ? rc : lt.total;
+}
+
+int64_t psig_logsig_out_size(const PsigLogDesc *desc)
+{
+    LevelTable lt;
+    const int rc = log_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    if (desc->lower_columns == nullptr && desc->n_lower_columns == 0) return lt.total;
+    if (desc->lower_columns == nullptr || desc->n_lower_columns < 0) return PSIG_ERR_SHAPE;
+    return desc->n_lower_columns + lt.size[lt.depth];
 }
 
 int psig_sig_forward(const PsigSigDesc *desc, const void *path, void *out, void *stream)
@@ -254,6 +289,7 @@ int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, 
     if (rc != PSIG_OK) return rc;
     if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
     if (!sig || !logsig || (!cache && psig_logsig_cache_size(desc) > 0)) return PSIG_ERR_NULL;
+    if (desc->lower_columns != nullptr && !horner_logsig_supported(*desc, lt)) return PSIG_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (desc->dtype == PSIG_F32)
         return generic_logsig_forward<float>(*desc, lt, static_cast<const float *>(sig), static_cast<float *>(logsig),
@@ -287,6 +323,7 @@ int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *c
     if (rc != PSIG_OK) return rc;
     if (desc->rows == 0 || lt.total == 0) return PSIG_OK;
     if (!sig || !grad_logsig || !grad_sig || (!cache && psig_logsig_cache_size(desc) > 0)) return PSIG_ERR_NULL;
+    if (desc->lower_columns != nullptr && !horner_logsig_supported(*desc, lt)) return PSIG_ERR_UNSUPPORTED;
     const int64_t need = psig_logsig_backward_workspace(desc);
     if (need > 0 && (!workspace || workspace_bytes < need)) return PSIG_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -64,6 +64,9 @@ bool tiled_supported(const PsigSigDesc &desc);
 template <typename T>
 int tiled_sig_forward(const PsigSigDesc &desc, const T *path, T *out, cudaStream_t stream);
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
+// Bounded wait of the bulk-copy staging: poll limit (test hook) and read-and-clear count of waits that ran out.
+int tiled_set_bulk_wait_polls(int polls);
+long long tiled_bulk_copy_timeouts();
 template <typename T>
 int tiled_sig_backward(const PsigSigDesc &desc, const T *path, const T *sig, const T *grad, T *grad_path,
                        void *workspace, cudaStream_t stream);
@@ -80,6 +83,17 @@ int closure_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
 long long closure_source(const PsigSigDesc &desc, const LevelTable &lt, int target_bins, char *buffer, long long capacity,
                          long long *stats);
 int closure_compile_only(const char *text, const char *arch, char *log, long long log_capacity);
+
+// Launch attributes of a kernel (opt-in dynamic shared memory above 48 KB, preference for the largest
+// shared-memory carveout) are properties of the function on a device: they are set the first time a
+// kernel is launched on a device, and again only when a launch needs more dynamic shared memory than
+// any launch before it -- not on every call.  Returns false when the runtime refuses.
+bool prepare_kernel_once(const void *kernel, size_t dynamic_smem, bool prefer_shared_carveout);
+template <typename Kernel>
+inline bool prepare_kernel(Kernel kernel, size_t dynamic_smem, bool prefer_shared_carveout)
+{
+    return prepare_kernel_once(reinterpret_cast<const void *>(kernel), dynamic_smem, prefer_shared_carveout);
+}
 
 // Called once after every kernel launch: counts the launch (psig_kernel_launches) and reports a
 // failed one.

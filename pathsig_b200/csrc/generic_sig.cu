@@ -441,7 +441,6 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
 #endif
 constexpr int kLaneWarps = PSIG_LANE_WARPS;
 constexpr int kLaneBlock = 32 * kLaneWarps;
-constexpr int kSmCount = 148;
 constexpr int kLaneShallow = 6;  // depths up to this run an instance with per-thread arrays of this size
 
 struct LaneUnit {  // per-unit facts, published once per unit group in shared memory
@@ -672,6 +671,10 @@ __global__ void increments_to_points(const T *__restrict__ inc_grad, T *__restri
 // stages the increments of its 32 units once for all its warps.
 int lane_warps_for(long long items, long long groups)
 {
+    int kSmCount = 148, device = 0, queried = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&queried, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && queried > 0)
+        kSmCount = queried;
     int best = kLaneWarps;
     long long best_cost = -1;
     for (int lw = kLaneWarps; lw >= 4; lw /= 2) {
@@ -780,7 +783,7 @@ int generic_sig_forward(const PsigSigDesc &desc, const LevelTable &lt, const T *
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
         auto launch = [&](auto kernel) {
             // the staged increments make shared memory the occupancy limit under the default L1 split
-            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            prepare_kernel(kernel, smem, true);
             kernel<<<grid, block, smem, stream>>>(plan, path, out);
         };
         if (single && shallow) launch(sig_forward_lanes<T, 1, kLaneShallow>);
@@ -817,10 +820,7 @@ int generic_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
         const size_t smem = 2 * sizeof(T) * 32 * (size_t)plan.lane_stride;
         const bool single = plan.lane_tb == 1, shallow = lt.depth <= kLaneShallow;
         auto launch = [&](auto kernel) {
-            if (smem > 48 * 1024 &&
-                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return;  // the launch below then fails and reports the error
-            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (!prepare_kernel(kernel, smem, true)) return;  // the launch below then fails and reports the error
             kernel<<<grid, block, smem, stream>>>(plan, path, sig, grad, inc_grad_ws);
         };
         if (single && shallow) launch(sig_backward_lanes<T, 1, kLaneShallow>);

@@ -72,6 +72,12 @@ struct HornerPlan {
     unsigned t_total;
     unsigned stage_top;  // backward: hold a dense image of the top degree of the incoming gradient in shared memory
     unsigned top_dense;  // d^N (0 when it does not fit 31 bits)
+    // Projected output: only these positions of the dense degrees below the top are written (forward) /
+    // carry an incoming gradient (backward), followed by the whole top degree.  nullptr: every position.
+    const long long *low_cols;
+    unsigned n_low;      // entries of low_cols
+    unsigned out_lower;  // columns of the output row ahead of the top degree: n_low, or `lower`
+    long long out_width;  // out_lower + top
 };
 
 // Four scalars moved as one access (16 bytes of float, 32 of double).
@@ -259,20 +265,30 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
-        T *l = logsig + row * p.width;
+        T *l = logsig + row * p.out_width;
         __syncthreads();  // the previous row's readers are done with the buffers
         for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) xs[i] = s[i];
         __syncthreads();
         const T *t1 = build_t<T, NMAX>(p, xs, ta, tb, nullptr);
         // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
-        if (N >= 2)
-            for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) l[i] = xs[i];
-        for_words_below_top<T, NMAX>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
+        if (p.low_cols != nullptr) {
+            // projected output: only the requested words below the top degree, each from its own splits
+            for (unsigned i = threadIdx.x; i < p.n_low; i += kHornerBlock) {
+                const unsigned pos = (unsigned)p.low_cols[i];
+                const int n = degree_at(p, pos, N - 1);
+                l[i] = xs[pos] + (n >= 2 ? split_sum(p, xs, t1, n, pos - p.off[n]) : T(0));
+            }
+        } else {
+            if (N >= 2)
+                for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) l[i] = xs[i];
+            for_words_below_top<T, NMAX>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
+        }
         if (p.top_words == nullptr && N >= 2) {
             // dense top degree: a thread takes a parent of degree N-1 and its d children
             const unsigned parents = p.dpow[N - 1];
             // 4 scalars per access when the runs of d children start on such boundaries
             const bool quads = (p.d & 3) == 0 && (p.lower & 3u) == 0 && (p.width & 3) == 0 &&
+                               (p.out_lower & 3u) == 0 && (p.out_width & 3) == 0 &&
                                (reinterpret_cast<uintptr_t>(sig) & (4 * sizeof(T) - 1)) == 0 &&
                                (reinterpret_cast<uintptr_t>(logsig) & (4 * sizeof(T) - 1)) == 0;
             if (quads) {
@@ -282,24 +298,24 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
                     const unsigned u = it / per_parent, a = 4u * (it - u * per_parent);
                     T acc[4];
                     PSIG_QUAD(N, p, xs, t1, u, a, acc)
-                    const size_t pos = p.lower + (size_t)u * p.d + a;
-                    const Quad<T> in = *reinterpret_cast<const Quad<T> *>(s + pos);
+                    const size_t pos = (size_t)u * p.d + a;
+                    const Quad<T> in = *reinterpret_cast<const Quad<T> *>(s + p.lower + pos);
                     Quad<T> o;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o.v[i] = in.v[i] + acc[i];
-                    *reinterpret_cast<Quad<T> *>(l + pos) = o;
+                    *reinterpret_cast<Quad<T> *>(l + p.out_lower + pos) = o;
                 }
             } else {
                 for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
                     const T *srun = s + p.lower + (size_t)u * p.d;
-                    T *lrun = l + p.lower + (size_t)u * p.d;
+                    T *lrun = l + p.out_lower + (size_t)u * p.d;
                     PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
                 }
             }
         } else {
             for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
                 const unsigned code = p.top_words ? (unsigned)p.top_words[i] : i;
-                l[p.lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
+                l[p.out_lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
             }
         }
     }
@@ -396,18 +412,26 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
-        const T *g = glog + row * p.width;
-        const T *gtop_global = g + p.lower;
+        const T *g = glog + row * p.out_width;
+        const T *gtop_global = g + p.out_lower;
         const T *gtop = p.stage_top ? gts : gtop_global;  // re-read N-1 times by each side of the adjoint
         T *out = gsig + row * p.width;
         __syncthreads();
         for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
             xs[i] = s[i];
-            const T gi = g[i];
+            const T gi = p.low_cols != nullptr ? T(0) : g[i];
             gl[i] = gi;
             gx[i] = gi;   // log S = x * 1 + ...: the degree-0 term of T_1 is 1
             ga[i] = T(0);  // build_t scratch first, then the adjoint of T_1
             gb[i] = T(0);
+        }
+        if (p.low_cols != nullptr) {
+            // projected gradient: spread it over the dense image of the lower degrees (a word may be
+            // requested twice), then start gx from it
+            __syncthreads();
+            for (unsigned i = threadIdx.x; i < p.n_low; i += kHornerBlock) atomicAdd(&gl[(unsigned)p.low_cols[i]], g[i]);
+            __syncthreads();
+            for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) gx[i] = gl[i];
         }
         // the top degree of x enters only through that same term
         if (p.stage_top && p.top_words != nullptr) {
@@ -556,6 +580,15 @@ int make_horner_plan(const PsigLogDesc &desc, const LevelTable &lt, HornerPlan *
     }
     p.t_total = t;
     p.stage_top = 0;
+    p.low_cols = nullptr;
+    p.n_low = 0;
+    if (desc.lower_columns != nullptr || desc.n_lower_columns > 0) {
+        if (desc.lower_columns == nullptr || desc.n_lower_columns < 0 || desc.n_lower_columns > 0x7fffffffLL) return PSIG_ERR_SHAPE;
+        p.low_cols = reinterpret_cast<const long long *>(desc.lower_columns);
+        p.n_low = (unsigned)desc.n_lower_columns;
+    }
+    p.out_lower = p.low_cols != nullptr ? p.n_low : p.lower;
+    p.out_width = (long long)p.out_lower + (long long)p.top;
     return PSIG_OK;
 }
 
@@ -586,11 +619,8 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
     if (rc != PSIG_OK) return rc;
     const size_t smem = forward_smem<T>(p);
     auto launch = [&](auto kernel) {
-        if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return (int)PSIG_ERR_CUDA;
         // rows in flight are limited by shared memory under the default L1 split
-        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
         kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
         return check_launch();
     };
@@ -613,10 +643,7 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
                    sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top_dense) <= kHornerMaxSmem / 2) ? 1u : 0u;
     const size_t smem = backward_smem<T>(p);
     auto launch = [&](auto kernel) {
-        if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return (int)PSIG_ERR_CUDA;
-        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
         kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
         return check_launch();
     };

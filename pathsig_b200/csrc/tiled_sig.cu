@@ -64,6 +64,20 @@ bool tiled_supported(const PsigSigDesc &desc)
 
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &) { return 0; }
 
+int tiled_set_bulk_wait_polls(int polls)
+{
+    const int rc = f32::bulk_wait_control(true, polls, nullptr);
+    return rc != PSIG_OK ? rc : f64::bulk_wait_control(true, polls, nullptr);
+}
+
+long long tiled_bulk_copy_timeouts()
+{
+    unsigned int a = 0, b = 0;
+    if (f32::bulk_wait_control(false, 0, &a) != PSIG_OK || f64::bulk_wait_control(false, 0, &b) != PSIG_OK)
+        return PSIG_ERR_CUDA;
+    return (long long)a + (long long)b;
+}
+
 template <>
 int tiled_sig_forward<float>(const PsigSigDesc &desc, const float *path, float *out, cudaStream_t stream)
 {

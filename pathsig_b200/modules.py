@@ -8,7 +8,10 @@ loads (``_windows``, ``_encoded_words``, ``_top_words``, ``_indices_from_sig``,
 
 ``LogSignature`` keeps the reference's composition (``modules.py:112-135``): signature in the
 hybrid layout (dense degrees below ``depth``, projected top degree), tensor logarithm in word
-coordinates, then a column gather for the projected case.
+coordinates, then the column selection of the projected case.  Where the row fits the shared-memory
+log-signature kernels, logarithm and selection are one kernel (``ops.logsig_projected``): only the
+requested columns are written, and the backward starts from the projected gradient; otherwise the
+selection is a stock gather after ``sig_to_logsig`` as in the reference.
 """
 from __future__ import annotations
 
@@ -17,7 +20,8 @@ from typing import List, Optional, Tuple
 import torch
 from torch import nn
 
-from .ops import compute_signature, sig_to_logsig
+from . import ops as ops_module
+from .ops import compute_signature, logsig_projected, logsig_projected_supported, sig_to_logsig
 from .projections import _default_device
 
 _MAX_DEPTH = 12
@@ -173,6 +177,18 @@ class LogSignature(nn.Module):
             raise ValueError(f"_indices_from_sig has a column outside [0, {width}).")
         # a projection that lists a word twice selects a column twice: those gradients must add up
         self._columns_repeat = len(set(host_columns)) != len(host_columns)
+        # The fused logarithm + selection writes "requested words below the top degree, then the whole top
+        # degree": that is the layout logsig_indices() gives; an index replaced through load_state_dict
+        # may not have it, and then the stock gather serves it.
+        lower = sum(self._ext_level_sizes[: self.depth])
+        top = int(self._ext_level_sizes[self.depth])
+        n_low = len(host_columns) - top
+        self._fusable = (n_low >= 0 and host_columns[n_low:] == list(range(lower, lower + top))
+                         and all(c < lower for c in host_columns[:n_low]))
+        device = self._indices_from_sig.device
+        self.register_buffer("_lower_columns", torch.tensor(host_columns[:n_low] if self._fusable else [],
+                                                            dtype=torch.int64, device=device), persistent=False)
+        self._fused_ok = {}
 
     def forward(self, path: torch.Tensor) -> torch.Tensor:
         if self.alternative_projection:
@@ -183,6 +199,13 @@ class LogSignature(nn.Module):
             level_sizes = [0] + [d ** k for k in range(1, self.depth + 1)]
         sig = compute_signature(path, self.depth, self.alternative_projection, self._top_words, level_sizes,
                                 self.use_windows, self._windows)
+        if self.alternative_projection and self._fusable:
+            key = (sig.dtype, ops_module._algo)  # the kernel family is a property of dtype, shape and selected algorithm
+            fused = self._fused_ok.get(key)
+            if fused is None:
+                fused = self._fused_ok[key] = logsig_projected_supported(sig.dtype, self.depth, d, level_sizes)
+            if fused:
+                return logsig_projected(sig, self.depth, d, self._top_words, level_sizes, self._lower_columns)
         logsig, _ = sig_to_logsig(sig, self.depth, d, self.alternative_projection, self._top_words, level_sizes)
         if not self.alternative_projection:
             return logsig

@@ -25,6 +25,7 @@ from torch import Tensor
 from . import _load
 
 __all__ = ["compute_signature", "sig_to_logsig", "signature_backward", "logsig_backward",
+           "logsig_projected", "logsig_projected_backward", "logsig_projected_supported",
            "chen_product", "chen_product_backward", "register_namespace", "NAMESPACE"]
 
 NAMESPACE = "pathsig_b200"
@@ -39,6 +40,13 @@ _SCHEMAS = {
                      "Tensor encoded_words, int[] level_sizes) -> (Tensor, Tensor)",
     "logsig_backward": "(Tensor signature_in, Tensor P_in, Tensor grad_logsig_in, int depth, "
                        "bool alternative_projection, Tensor encoded_words, int[] level_sizes) -> Tensor",
+    # not in the reference, where a stock index_select follows the logarithm (src/pathsig/modules.py:134-135):
+    # logarithm and column selection as one kernel.  The output row is the words of the degrees below `depth`
+    # listed in lower_columns (positions in a dense row of those degrees) followed by the whole top degree.
+    "logsig_projected": "(Tensor signature_in, int depth, int d, Tensor top_words, int[] level_sizes, "
+                        "Tensor lower_columns) -> Tensor",
+    "logsig_projected_backward": "(Tensor signature_in, Tensor grad_out, int depth, int d, Tensor top_words, "
+                                 "int[] level_sizes, Tensor lower_columns) -> Tensor",
     # not in the reference: Chen product of two dense truncated signatures and its adjoint
     "chen_product": "(Tensor sig_a, Tensor sig_b, int depth, int d) -> Tensor",
     "chen_product_backward": "(Tensor sig_a, Tensor sig_b, Tensor grad_out, int depth, int d) -> (Tensor, Tensor)",
@@ -207,6 +215,34 @@ def _log_desc(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: T
     return desc
 
 
+def _projected_log_desc(signature: Tensor, depth: int, d: int, top_words: Tensor, level_sizes: Sequence[int],
+                        lower_columns: Tensor, fake: bool = False) -> _load.LogDesc:
+    """``PsigLogDesc`` of the fused logarithm + column selection."""
+    desc = _log_desc(signature, depth, d, True, top_words, level_sizes, fake=fake)
+    if lower_columns.dim() != 1 or lower_columns.dtype != torch.int64:
+        raise RuntimeError("lower_columns must be a 1D int64 tensor")
+    if not fake:
+        if not lower_columns.is_cuda or not lower_columns.is_contiguous():
+            raise RuntimeError("lower_columns must be a contiguous CUDA tensor")
+        _check_same_device(signature, lower_columns=lower_columns)
+    desc.n_lower_columns = lower_columns.numel()
+    # a non-null marker is enough for the shape queries; an empty list still selects the projected layout
+    desc.lower_columns = (lower_columns.data_ptr() if not fake and lower_columns.numel() > 0 else 1)
+    return desc
+
+
+def logsig_projected_supported(dtype: torch.dtype, depth: int, d: int, level_sizes: Sequence[int]) -> bool:
+    """Whether the fused logarithm + column selection has a kernel for this row (it is part of the
+    row-in-shared-memory family, so the dense degrees below the top must fit shared memory)."""
+    lib = _load.ensure_loaded()
+    desc = _load.LogDesc()
+    desc.dtype = _load.PSIG_F32 if dtype == torch.float32 else _load.PSIG_F64
+    desc.d, desc.depth, desc.algo, desc.rows = int(d), int(depth), _algo, 1
+    desc.top_size = int(level_sizes[depth])
+    desc.top_words = 1 if desc.top_size != int(d) ** int(depth) else None
+    return lib.psig_logsig_cache_size(ctypes.byref(desc)) == 0
+
+
 def _row_width(d: int, depth: int, alt: bool, level_sizes: Sequence[int]) -> int:
     if alt:
         return int(sum(int(s) for s in level_sizes[1: depth + 1]))
@@ -333,6 +369,51 @@ def _logsig_backward_cuda(signature_in, P_in, grad_logsig_in, depth, alternative
         rc = lib.psig_logsig_backward(ctypes.byref(desc), _ptr(sig), _ptr(cache), _ptr(grad), _ptr(grad_sig),
                                       _ptr(ws), int(ws_bytes), _stream_ptr(sig.device))
     _load.check(rc, "logsig_backward")
+    return grad_sig
+
+
+def _logsig_projected_cuda(signature_in, depth, d, top_words, level_sizes, lower_columns):
+    lib = _load.ensure_loaded()
+    if not signature_in.is_cuda:
+        raise RuntimeError("signature must be CUDA")
+    sig = signature_in.contiguous()
+    desc = _projected_log_desc(sig, depth, d, top_words, level_sizes, lower_columns)
+    with torch.cuda.device(sig.device):
+        S = lib.psig_logsig_size(ctypes.byref(desc))
+        _load.check(S, "logsig_projected")
+        if S != sig.size(-1):
+            raise RuntimeError(f"signature width {sig.size(-1)} does not match the layout width {S}")
+        width = lib.psig_logsig_out_size(ctypes.byref(desc))
+        _load.check(width, "logsig_projected")
+        out = torch.empty(sig.shape[:-1] + (int(width),), dtype=sig.dtype, device=sig.device)
+        if out.numel() == 0:
+            return out
+        rc = lib.psig_logsig_forward(ctypes.byref(desc), _ptr(sig), _ptr(out), None, _stream_ptr(sig.device))
+    _load.check(rc, "logsig_projected")
+    return out
+
+
+def _logsig_projected_backward_cuda(signature_in, grad_out, depth, d, top_words, level_sizes, lower_columns):
+    lib = _load.ensure_loaded()
+    if not signature_in.is_cuda or not grad_out.is_cuda:
+        raise RuntimeError("signature and grad_out must be CUDA")
+    if grad_out.dtype != signature_in.dtype:
+        raise RuntimeError("grad_out must have same dtype as signature")
+    _check_same_device(signature_in, grad_out=grad_out)
+    sig = signature_in.contiguous()
+    grad = grad_out.contiguous()
+    desc = _projected_log_desc(sig, depth, d, top_words, level_sizes, lower_columns)
+    with torch.cuda.device(sig.device):
+        width = lib.psig_logsig_out_size(ctypes.byref(desc))
+        _load.check(width, "logsig_projected_backward")
+        if tuple(grad.shape) != tuple(sig.shape[:-1]) + (int(width),):
+            raise RuntimeError("grad_out must be [B,(W),n_lower_columns + top_size]")
+        grad_sig = torch.empty_like(sig)
+        if grad_sig.numel() == 0:
+            return grad_sig
+        rc = lib.psig_logsig_backward(ctypes.byref(desc), _ptr(sig), None, _ptr(grad), _ptr(grad_sig), None, 0,
+                                      _stream_ptr(sig.device))
+    _load.check(rc, "logsig_projected_backward")
     return grad_sig
 
 
@@ -486,6 +567,21 @@ def _fake_logsig_backward(signature, P_arr, grad_logsig, depth, alternative_proj
     return torch.empty_like(signature)
 
 
+def _fake_logsig_projected(signature, depth, d, top_words, level_sizes, lower_columns):
+    torch._check(signature.dtype in (torch.float32, torch.float64), lambda: "signature must be float32 or float64")
+    torch._check(signature.dim() in (2, 3), lambda: "signature must be 2D or 3D")
+    torch._check(1 <= int(depth) <= 12, lambda: "depth must satisfy 1 <= depth <= 12")
+    torch._check(len(level_sizes) >= int(depth) + 1, lambda: "level_sizes must have entries up to depth")
+    torch._check(lower_columns.dim() == 1, lambda: "lower_columns must be 1D")
+    width = lower_columns.shape[0] + int(level_sizes[int(depth)])
+    return signature.new_empty(tuple(signature.shape[:-1]) + (width,))
+
+
+def _fake_logsig_projected_backward(signature, grad_out, depth, d, top_words, level_sizes, lower_columns):
+    torch._check(grad_out.dtype == signature.dtype, lambda: "grad_out must have same dtype as signature")
+    return torch.empty_like(signature)
+
+
 def _fake_chen_product(sig_a, sig_b, depth, d):
     torch._check(sig_a.dtype in (torch.float32, torch.float64), lambda: "signatures must be float32 or float64")
     torch._check(sig_a.dtype == sig_b.dtype, lambda: "signatures must have the same dtype")
@@ -508,6 +604,8 @@ _IMPLS = {
     "signature_backward": (_signature_backward_cuda, _fake_signature_backward),
     "sig_to_logsig": (_sig_to_logsig_cuda, _fake_sig_to_logsig),
     "logsig_backward": (_logsig_backward_cuda, _fake_logsig_backward),
+    "logsig_projected": (_logsig_projected_cuda, _fake_logsig_projected),
+    "logsig_projected_backward": (_logsig_projected_backward_cuda, _fake_logsig_projected_backward),
     "chen_product": (_chen_product_cuda, _fake_chen_product),
     "chen_product_backward": (_chen_product_backward_cuda, _fake_chen_product_backward),
 }
@@ -554,6 +652,19 @@ def register_namespace(ns: str) -> None:
                 signature, cache, grad_logsig, ctx.depth, ctx.alt, encoded_words, ctx.level_sizes)
         return grad_sig, None, None, None, None, None
 
+    def setup_logproj(ctx, inputs, output):
+        signature, depth, d, top_words, level_sizes, lower_columns = inputs
+        ctx.save_for_backward(signature, top_words, lower_columns)
+        ctx.depth, ctx.d, ctx.level_sizes = int(depth), int(d), level_sizes
+
+    def backward_logproj(ctx, grad_out):
+        signature, top_words, lower_columns = ctx.saved_tensors
+        grad_sig = None
+        if ctx.needs_input_grad[0]:
+            grad_sig = getattr(torch.ops, ns).logsig_projected_backward.default(
+                signature, grad_out, ctx.depth, ctx.d, top_words, ctx.level_sizes, lower_columns)
+        return grad_sig, None, None, None, None, None
+
     def setup_chen(ctx, inputs, output):
         sig_a, sig_b, depth, d = inputs
         ctx.save_for_backward(sig_a, sig_b)
@@ -598,6 +709,7 @@ def register_namespace(ns: str) -> None:
                                     setup_context=setup_chen_bwd, lib=lib)
     torch.library.register_autograd(f"{ns}::compute_signature", backward_sig, setup_context=setup_sig, lib=lib)
     torch.library.register_autograd(f"{ns}::sig_to_logsig", backward_log, setup_context=setup_log, lib=lib)
+    torch.library.register_autograd(f"{ns}::logsig_projected", backward_logproj, setup_context=setup_logproj, lib=lib)
     _libraries[ns] = lib
 
 
@@ -624,6 +736,20 @@ def signature_backward(path: Tensor, signature: Tensor, grad_signature: Tensor, 
     """dL/dpath from dL/dsignature."""
     return _ops.signature_backward.default(path, signature, grad_signature, depth, alternative_projection,
                                            encoded_words, level_sizes, use_windows, windows)
+
+
+def logsig_projected(signature: Tensor, depth: int, d: int, top_words: Tensor, level_sizes: List[int],
+                     lower_columns: Tensor) -> Tensor:
+    """Signature (hybrid layout) -> projected log-signature: the words of the degrees below ``depth`` at
+    ``lower_columns`` followed by the whole top degree, in one kernel.  Differentiable wrt ``signature``."""
+    return _ops.logsig_projected.default(signature, depth, d, top_words, level_sizes, lower_columns)
+
+
+def logsig_projected_backward(signature: Tensor, grad_out: Tensor, depth: int, d: int, top_words: Tensor,
+                              level_sizes: List[int], lower_columns: Tensor) -> Tensor:
+    """dL/dsignature from the gradient of :func:`logsig_projected`'s output."""
+    return _ops.logsig_projected_backward.default(signature, grad_out, depth, d, top_words, level_sizes,
+                                                  lower_columns)
 
 
 def chen_product(sig_a: Tensor, sig_b: Tensor, depth: int, d: int) -> Tensor:

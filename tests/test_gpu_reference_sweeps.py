@@ -7,6 +7,10 @@ random directions, and gradient error at three time steps (tests/test_sig.py:73-
 tests/test_logsig.py:75-154 of the reference).  Here the same sweeps, inputs, metrics and tolerances are
 applied to this library in both dtypes, with the reference's operators (compiled unchanged,
 ``oracle/_ref``) evaluated in float64 on the same inputs in the place of the third-party oracle.
+The dot-product metric divides by a sum in which the gradient's few large entries cancel, so at some
+shapes it magnifies float32 rounding past the reference's bound for ANY float32 implementation; the
+reference's own float32 result is therefore put through the same metric, and a bound is
+max(the reference's tolerance, twice what the reference itself reaches).
 Skipped when that build is absent.
 """
 from __future__ import annotations
@@ -87,7 +91,9 @@ def _compare_signature(ps, ref, B, T, d, depth, dtype):
     x64, G64 = x.double(), G.double()
     ref_out = ref.compute_signature(x64, depth, False, nowords, [], False, nowin)
     ref_grad = ref.signature_backward(x64, ref_out, G64, depth, False, nowords, [], False, nowin)
-    return _metrics(out.detach(), xa.grad, ref_out, ref_grad, T)
+    own_out = ref.compute_signature(x, depth, False, nowords, [], False, nowin)
+    own_grad = ref.signature_backward(x, own_out, G, depth, False, nowords, [], False, nowin)
+    return _metrics(out.detach(), xa.grad, ref_out, ref_grad, T), _metrics(own_out, own_grad, ref_out, ref_grad, T)
 
 
 def _compare_logsignature(ps, ref, B, T, d, depth, dtype):
@@ -105,13 +111,21 @@ def _compare_logsignature(ps, ref, B, T, d, depth, dtype):
     g_full = torch.zeros_like(logsig).index_add_(-1, idx, G.double())
     g_sig = ref.logsig_backward(sig, cache, g_full, depth, True, tw, ls)
     ref_grad = ref.signature_backward(x64, sig, g_sig, depth, True, tw, ls, False, nowin)
-    return _metrics(out.detach(), xa.grad, logsig.index_select(-1, idx), ref_grad, T)
+    sig32 = ref.compute_signature(x, depth, True, tw, ls, False, nowin)
+    logsig32, cache32 = ref.sig_to_logsig(sig32, depth, d, True, tw, ls)
+    g_full32 = torch.zeros_like(logsig32).index_add_(-1, idx, G)
+    own_grad = ref.signature_backward(x, sig32, ref.logsig_backward(sig32, cache32, g_full32, depth, True, tw, ls),
+                                      depth, True, tw, ls, False, nowin)
+    want = logsig.index_select(-1, idx)
+    return (_metrics(out.detach(), xa.grad, want, ref_grad, T),
+            _metrics(logsig32.index_select(-1, idx), own_grad, want, ref_grad, T))
 
 
-def _assert(res, tol_fwd, tol_rel):
-    assert res["fwd"] < tol_fwd, res
-    assert res["grad_dot"] < tol_rel, res
-    assert res["grad_timestep"] < tol_rel, res
+def _assert(both, tol_fwd, tol_rel):
+    res, reference_itself = both
+    assert res["fwd"] < max(tol_fwd, 2 * reference_itself["fwd"]), both
+    assert res["grad_dot"] < max(tol_rel, 2 * reference_itself["grad_dot"]), both
+    assert res["grad_timestep"] < max(tol_rel, 2 * reference_itself["grad_timestep"]), both
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
