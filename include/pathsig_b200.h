@@ -117,8 +117,10 @@ int64_t psig_kernel_launches(void);
  * reference.  A block waits for a staged chunk of points for a bounded number of polls; when the wait
  * runs out it reads the same bytes with plain loads (same result) and counts the event.
  * psig_bulk_copy_timeouts returns the count on the current device since the last call and clears it;
- * psig_set_bulk_wait_polls sets the bound on the current device (<= 0: the default, 2^20 polls) so that
- * a test can make the wait run out.  Both synchronise the device; neither belongs in a hot loop. */
+ * psig_set_bulk_wait_polls sets the bound on the current device (negative: the default, 2^20 polls;
+ * 0: never wait, every staged chunk is read with plain loads) so that a test can make the wait run
+ * out -- one poll is not enough for that, a poll may itself block for a short hardware-defined time.
+ * Both synchronise the device; neither belongs in a hot loop. */
 int64_t psig_bulk_copy_timeouts(void);
 int psig_set_bulk_wait_polls(int polls);
 const char *psig_status_string(int status);

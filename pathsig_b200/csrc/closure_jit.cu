@@ -1049,10 +1049,13 @@ int launch(const Plan &plan, const PassPlan &pass, LaunchParams<T> &p, long long
     // scheduler runs fastest), at most kMaxGroupsPerBlock
     int ng = 1;
     while (ng < kMaxGroupsPerBlock && (groups + ng - 1) / ng * bin_blocks > sms) ng *= 2;
+    // `buffers` rows of about chunk*d scalars per unit: two buffers of points, plus the gradients in backward;
+    // wide paths take fewer groups per block so that a chunk still holds a few steps
+    auto chunk_for = [&](int g) { return (long long)(kStageBytes / (sizeof(T) * 32 * g * (size_t)plan.d * buffers)) - 1; };
+    while (ng > 1 && chunk_for(ng) < 4) ng /= 2;
     const long long unit_blocks = (groups + ng - 1) / ng;
     const int rows = 32 * ng;
-    // `buffers` rows of about chunk*d scalars per unit: two buffers of points, plus the gradients in backward
-    long long chunk = (long long)(kStageBytes / (sizeof(T) * rows * (size_t)plan.d * buffers)) - 1;
+    long long chunk = chunk_for(ng);
     if (chunk < 1) return PSIG_ERR_TOO_LARGE;
     p.chunk = (int)std::min(chunk, 32LL);
     p.stride = ((p.chunk + 1) * plan.d) | 1;
@@ -1100,11 +1103,16 @@ bool closure_supported(const PsigSigDesc &desc, const LevelTable &lt)
     return plan && plan->usable;
 }
 
-// Cheap test (no compilation) used by the automatic selection: projected rows with a host copy of the
-// codes, a closure of moderate size and enough work to repay the one-off compilation.
+// Cheap test (no compilation) used by the automatic selection: dense rows, or projected rows with a host
+// copy of the codes; a closure of moderate size; enough work to repay the one-off compilation; and
+// channels few enough that a chunk of staged points fits shared memory.
 bool closure_worthwhile(const PsigSigDesc &desc, const LevelTable &lt)
 {
-    if (!desc.projected || !desc.words_host) return false;
+    bool listed = false;
+    long long d_pow = 1;
+    for (int k = 1; k <= lt.depth; ++k) { d_pow *= lt.d; listed = listed || lt.size[k] != d_pow; }
+    if (listed && !desc.words_host) return false;
+    if (lt.d > 64) return false;
     const long long units = desc.B * (desc.W > 0 ? desc.W : 1);
     if (units < 256) return false;
     long long words = 0;

@@ -344,9 +344,9 @@ def test_loaded_column_index_with_repeats_keeps_every_gradient(ps):
 
 def test_bounded_wait_of_the_bulk_staging_runs_out_harmlessly(ps, oracle):
     """The tiled forward stages long un-windowed paths with bulk copies and waits for each chunk a bounded
-    number of polls.  With the bound lowered to a single poll the wait runs out (nothing can have landed
-    yet), the blocks fall back to plain loads of the same bytes and count the event; results are
-    unchanged.  The bound is restored afterwards."""
+    number of polls.  With the bound lowered to zero polls the wait runs out at once, the blocks fall back
+    to plain loads of the same bytes and count the event; results are unchanged.  The bound is restored
+    afterwards."""
     from pathsig_b200 import _load
     lib = _load.ensure_loaded()
     x = util.brownian_path(6, 300, 8, seed=4, dtype=torch.float32)     # 299 steps: five chunks of 64
@@ -358,12 +358,12 @@ def test_bounded_wait_of_the_bulk_staging_runs_out_harmlessly(ps, oracle):
     torch.cuda.synchronize()
     assert lib.psig_bulk_copy_timeouts() == 0                          # copies land in time normally
     try:
-        assert lib.psig_set_bulk_wait_polls(1) == 0
+        assert lib.psig_set_bulk_wait_polls(0) == 0
         out_short = sig(x.to(DEV))
         torch.cuda.synchronize()
         missed = lib.psig_bulk_copy_timeouts()
     finally:
-        assert lib.psig_set_bulk_wait_polls(0) == 0
+        assert lib.psig_set_bulk_wait_polls(-1) == 0
     assert missed > 0
     widths = util.level_widths(8, 4)
     assert max(util.level_rel_errors(out_short, want, widths)) < 1e-5

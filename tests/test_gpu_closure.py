@@ -137,3 +137,28 @@ def test_repeated_word_falls_back(ps, oracle):
             ps.Signature(depth=3, projection=proj)(x.to(DEV))
     finally:
         ps.ops.set_algorithm("auto")
+
+
+@pytest.mark.parametrize("d,depth", [(3, 4), (40, 2)])
+def test_dense_shape_without_a_tiled_instance_takes_the_closure_kernels(ps, d, depth):
+    """Dense rows of a shape the register-tiled table does not hold, with enough work: the automatic
+    selection specialises closure kernels for the shape; the result matches the generic kernels."""
+    x = util.brownian_path(2048, 128, d, seed=11, dtype=torch.float32).to(DEV)
+    mod = ps.Signature(depth=depth)
+
+    def run(algo):
+        ps.ops.set_algorithm(algo)
+        try:
+            xa = x.clone().requires_grad_(True)
+            out = mod(xa)
+            out.backward(torch.ones_like(out))
+            return out.detach(), xa.grad
+        finally:
+            ps.ops.set_algorithm("auto")
+
+    out_a, grad_a = run("auto")
+    out_c, grad_c = run("closure")
+    out_g, grad_g = run("generic")
+    assert torch.equal(out_a, out_c)
+    assert max(util.level_rel_errors(out_c, out_g, util.level_widths(d, depth))) < 1e-5
+    assert util.rel_error(grad_c, grad_g) < 1e-5
