@@ -2,8 +2,8 @@
 
 Same public surface as the reference package (``src/pathsig/__init__.py:1-8``):
 ``Signature``, ``LogSignature`` and the ``projections`` namespace.  Importing the package
-loads the CUDA library and registers the operators; it fails loudly when the library has not
-been built.  :func:`install_as_pathsig` additionally exposes the package under the name
+loads the CUDA library and the compiled operator registration; it fails loudly when either has
+not been built.  :func:`install_as_pathsig` additionally exposes the package under the name
 ``pathsig`` for code written against the reference.
 """
 from ._load import ensure_loaded as _ensure_loaded

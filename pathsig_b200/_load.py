@@ -1,8 +1,9 @@
-"""Loads ``libpathsig_b200.so`` (the CUDA library behind the C ABI of ``include/pathsig_b200.h``).
+"""Loads ``libpathsig_b200.so`` (the CUDA library behind the C ABI of ``include/pathsig_b200.h``) and
+``libpathsig_b200_torch.so`` (the operator registration with the PyTorch dispatcher on top of it).
 
 Counterpart of the reference's loader (``src/pathsig/_load.py:12-45``): one lock-guarded load
-per process, a clear error when the native library is missing.  There is no CPU or PyTorch
-fallback: without the library every operator raises.
+per process, a clear error when a native library is missing.  There is no CPU or PyTorch
+fallback: without the libraries every operator raises.
 """
 from __future__ import annotations
 
@@ -13,6 +14,8 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libpathsig_b200.so"
 LIB_PATH = os.path.join(_HERE, LIB_NAME)
+BINDING_NAME = "libpathsig_b200_torch.so"
+BINDING_PATH = os.path.join(_HERE, BINDING_NAME)
 MAX_DEPTH = 12
 ABI_VERSION = 2
 
@@ -21,6 +24,7 @@ ALGO_AUTO, ALGO_GENERIC, ALGO_TILED, ALGO_CLOSURE = 0, 1, 2, 3
 
 _lock = threading.Lock()
 _lib = None
+_binding = None
 
 
 class SigDesc(ctypes.Structure):
@@ -120,6 +124,33 @@ def ensure_loaded() -> ctypes.CDLL:
             raise RuntimeError(f"pathsig_b200: {LIB_NAME} has ABI {lib.psig_abi_version()}, expected {ABI_VERSION}; rebuild it.")
         _lib = lib
     return _lib
+
+
+def ensure_binding_loaded() -> ctypes.CDLL:
+    """Load the compiled operator registration once (``torch.ops.pathsig_b200.*`` exist afterwards);
+    returns a handle for its two plain-C controls."""
+    global _binding
+    if _binding is not None:
+        return _binding
+    ensure_loaded()
+    with _lock:
+        if _binding is not None:
+            return _binding
+        if not os.path.isfile(BINDING_PATH):
+            raise RuntimeError(
+                f"pathsig_b200: operator library {BINDING_PATH} not found. Build it with "
+                "`python -c 'import __graft_entry__ as g; g.build()'` or `make -C pathsig_b200/csrc`. "
+                "There is no Python fallback for the operators."
+            )
+        import torch
+        torch.ops.load_library(BINDING_PATH)
+        binding = ctypes.CDLL(BINDING_PATH)
+        binding.psig_torch_set_algorithm.restype = None
+        binding.psig_torch_set_algorithm.argtypes = [ctypes.c_int]
+        binding.psig_torch_get_algorithm.restype = ctypes.c_int
+        binding.psig_torch_get_algorithm.argtypes = []
+        _binding = binding
+    return _binding
 
 
 def check(status: int, what: str) -> None:

@@ -1,23 +1,24 @@
 """Operator layer: the reference's four operators, served by the B200 CUDA library.
 
-Host-side mirror of ``src/pathsig/ops.py`` and ``src/pathsig/bindings.cpp`` of the reference:
-the same four schemas (``bindings.cpp:9-63``), the same fake (meta) shape functions
-(``ops.py:59-84, 101-123, 152-179, 197-227``) and the same autograd wiring
-(``ops.py:231-297``).  The CUDA implementations validate like the reference launchers
-(``forward/sig_launch.cu:84-121``, ``backward/sig_backward_launch.cu:94-155``), allocate the
-outputs with torch's caching allocator and hand raw pointers plus the current stream to the
-C ABI (``include/pathsig_b200.h``).  torch is used for memory, streams and dispatch only.
+Host-side mirror of ``src/pathsig/ops.py`` of the reference: thin wrappers around the dispatcher
+entries, the same fake (meta) shape functions (``ops.py:59-84, 101-123, 152-179, 197-227``) and the
+same autograd wiring (``ops.py:231-297``).  The operators themselves -- the four schemas of
+``src/pathsig/bindings.cpp:9-63`` plus the projected log-signature and the Chen product, registered
+for the CUDA key only -- live in the compiled library ``libpathsig_b200_torch.so``
+(``csrc/torch_binding.cpp``), which validates like the reference launchers, allocates outputs with
+torch's caching allocator and hands raw pointers plus the current stream to the C ABI
+(``include/pathsig_b200.h``).  torch is used for memory, streams and dispatch only.
 
 The operators are registered in the namespace ``pathsig_b200`` so that this package and a
 build of the reference (namespace ``pathsig``) can live in one process, which is how the
-parity tests compare them.  :func:`register_namespace` registers the same operators under
-another namespace (``pathsig_b200.install_as_pathsig`` uses it for ``pathsig``).
+parity tests compare them.  :func:`register_namespace` defines the same operators under
+another namespace (``pathsig_b200.install_as_pathsig`` uses it for ``pathsig``), forwarding to
+the compiled ones.
 """
 from __future__ import annotations
 
-import collections
 import ctypes
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 from torch import Tensor
@@ -52,8 +53,9 @@ _SCHEMAS = {
     "chen_product_backward": "(Tensor sig_a, Tensor sig_b, Tensor grad_out, int depth, int d) -> (Tensor, Tensor)",
 }
 
-# Kernel family used by the signature operators: _load.ALGO_AUTO / ALGO_GENERIC / ALGO_TILED.
-# Tests flip it to compare the register-tiled kernels with the generic ones.
+# Kernel family used by the signature operators: _load.ALGO_AUTO / ALGO_GENERIC / ALGO_TILED / ALGO_CLOSURE.
+# Tests flip it to compare the register-tiled kernels with the generic ones.  The compiled operator layer
+# holds the value it acts on; this copy serves the shape queries made from Python.
 _algo = _load.ALGO_AUTO
 
 
@@ -62,33 +64,11 @@ def set_algorithm(name: str) -> None:
     global _algo
     _algo = {"auto": _load.ALGO_AUTO, "generic": _load.ALGO_GENERIC, "tiled": _load.ALGO_TILED,
              "closure": _load.ALGO_CLOSURE}[name]
-
-
-# Host copies of word-code tensors.  The prefix-closure kernels are generated from the word set, so the
-# library wants the codes in host memory; reading them back on every call would synchronise, so the
-# copy is made once per (storage, version) and kept while the device tensor is alive.  An entry holds a
-# reference to its device tensor, which keeps the address from being reused by another tensor.
-_HOST_WORDS_LIMIT = 64
-_host_words_cache: "collections.OrderedDict" = collections.OrderedDict()
-
-
-def _host_words(words: Tensor) -> Optional[Tensor]:
-    key = (words.data_ptr(), words._version, words.numel(), words.device.index)
-    hit = _host_words_cache.get(key)
-    if hit is not None:
-        _host_words_cache.move_to_end(key)
-        return hit[1]
-    if torch.cuda.is_current_stream_capturing():
-        return None  # no device read inside a graph capture; the library then uses another kernel family
-    host = words.detach().cpu().contiguous()
-    _host_words_cache[key] = (words, host)
-    while len(_host_words_cache) > _HOST_WORDS_LIMIT:
-        _host_words_cache.popitem(last=False)
-    return host
+    _load.ensure_binding_loaded().psig_torch_set_algorithm(_algo)
 
 
 # --------------------------------------------------------------------------------------
-# helpers
+# helpers of the shape queries
 # --------------------------------------------------------------------------------------
 
 def _dtype_id(t: Tensor) -> int:
@@ -99,135 +79,26 @@ def _dtype_id(t: Tensor) -> int:
     raise RuntimeError("path must be float32 or float64")
 
 
-def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-
-
-def _ptr(t: Tensor) -> ctypes.c_void_p:
-    return ctypes.c_void_p(t.data_ptr() if t.numel() > 0 else 0)
-
-
-def _check_same_device(anchor: Tensor, **operands: Tensor) -> None:
-    """Every tensor operand must live on the device the kernels are launched on (the anchor's).  The
-    dispatcher does not check this for operators registered from Python, and a pointer into another
-    GPU's memory would fault there (or be read silently over a peer mapping)."""
-    for name, t in operands.items():
-        if t.device != anchor.device:
-            raise RuntimeError(f"{name} must be on the same device as the path/signature "
-                               f"({name} is on {t.device}, expected {anchor.device})")
-
-
-def _check_words_cuda(encoded_words: Tensor) -> None:
-    if not encoded_words.is_cuda:
-        raise RuntimeError("encoded_words must be CUDA")
-    if encoded_words.dtype != torch.int64:
-        raise RuntimeError("encoded_words must be int64")
-    if not encoded_words.is_contiguous():
-        raise RuntimeError("encoded_words must be contiguous")
-    if encoded_words.dim() != 1:
-        raise RuntimeError("encoded_words must be 1D")
-
-
-def _sig_desc(path: Tensor, depth: int, alt: bool, encoded_words: Tensor, level_sizes: Sequence[int],
-              use_windows: bool, windows: Tensor) -> Tuple[_load.SigDesc, list]:
-    """Validated ``PsigSigDesc`` plus the tensors that must stay alive during the call."""
-    if not path.is_cuda:
-        raise RuntimeError("path must be CUDA")
-    if path.dim() != 3:
-        raise RuntimeError("path must be [B,T,d]")
-    depth = int(depth)
-    if not (1 <= depth <= _load.MAX_DEPTH):
-        raise RuntimeError("depth must be in [1,12]")
-    B, L, d = path.shape
-    if L < 2:
-        raise RuntimeError("path must have at least 2 time steps")
-    keep = []
-    desc = _load.SigDesc()
-    desc.dtype = _dtype_id(path)
-    desc.d, desc.depth, desc.B, desc.L = d, depth, B, L
-    desc.projected = 1 if alt else 0
-    desc.algo = _algo
-    if alt:
-        _check_words_cuda(encoded_words)
-        _check_same_device(path, encoded_words=encoded_words)
-        if len(level_sizes) < depth + 1:
-            raise RuntimeError("level_sizes must cover at least depth + 1 entries")
-        need = 0
-        for k in range(1, depth + 1):
-            size = int(level_sizes[k])
-            desc.level_sizes[k] = size
-            if size != d ** k:
-                need += size
-        if encoded_words.numel() < need:
-            raise RuntimeError("encoded_words holds fewer codes than level_sizes requires")
-        desc.words = encoded_words.data_ptr() if encoded_words.numel() > 0 else None
-        keep.append(encoded_words)
-        if encoded_words.numel() > 0:
-            host = _host_words(encoded_words)
-            if host is not None:
-                desc.words_host = host.data_ptr()
-                keep.append(host)
-    if use_windows:
-        if not windows.is_cuda:
-            raise RuntimeError("windows must be CUDA")
-        if windows.dim() != 2 or windows.size(1) != 2:
-            raise RuntimeError("windows must be [W,2]")
-        if windows.dtype not in (torch.int32, torch.int64):
-            raise RuntimeError("windows must be int32")
-        _check_same_device(path, windows=windows)
-        win = windows.to(torch.int32).contiguous()
-        keep.append(win)
-        desc.W = win.size(0)
-        desc.windows = win.data_ptr() if win.numel() > 0 else None
-    return desc, keep
-
-
-def _log_desc(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: Tensor,
-              level_sizes: Sequence[int], fake: bool = False) -> _load.LogDesc:
-    """``PsigLogDesc`` for these arguments; with ``fake`` no device pointer is read (shape queries only)."""
+def _log_desc_for_shapes(signature: Tensor, depth: int, d: int, alt: bool, encoded_words: Tensor,
+                         level_sizes: Sequence[int]) -> _load.LogDesc:
+    """``PsigLogDesc`` for host-only shape queries (fake tensors): no device pointer is read."""
     depth, d = int(depth), int(d)
     if not (1 <= depth <= _load.MAX_DEPTH):
         raise RuntimeError("depth must be in [1,12]")
     if d < 1:
         raise RuntimeError("d must be >= 1")
-    if signature.dim() not in (2, 3):
-        raise RuntimeError("signature must be [B,S] or [B,W,S]")
     desc = _load.LogDesc()
     desc.dtype = _dtype_id(signature)
     desc.d, desc.depth = d, depth
     desc.algo = _algo
-    desc.rows = 0 if fake else (signature.numel() // signature.size(-1) if signature.size(-1) > 0 else 0)
+    desc.rows = 0
     desc.top_size = d ** depth
     if alt:
-        if not fake:
-            _check_words_cuda(encoded_words)
-            _check_same_device(signature, encoded_words=encoded_words)
         if len(level_sizes) < depth + 1:
             raise RuntimeError("level_sizes must have entries up to depth")
         desc.top_size = int(level_sizes[depth])
         if desc.top_size != d ** depth:
-            if encoded_words.numel() < desc.top_size:
-                raise RuntimeError("encoded_words holds fewer codes than level_sizes[depth]")
-            if fake:
-                desc.top_words = 1 if encoded_words.numel() > 0 else None  # non-null marker, never read
-            else:
-                desc.top_words = encoded_words.data_ptr() if encoded_words.numel() > 0 else None
-    return desc
-
-
-def _projected_log_desc(signature: Tensor, depth: int, d: int, top_words: Tensor, level_sizes: Sequence[int],
-                        lower_columns: Tensor, fake: bool = False) -> _load.LogDesc:
-    """``PsigLogDesc`` of the fused logarithm + column selection."""
-    desc = _log_desc(signature, depth, d, True, top_words, level_sizes, fake=fake)
-    if lower_columns.dim() != 1 or lower_columns.dtype != torch.int64:
-        raise RuntimeError("lower_columns must be a 1D int64 tensor")
-    if not fake:
-        if not lower_columns.is_cuda or not lower_columns.is_contiguous():
-            raise RuntimeError("lower_columns must be a contiguous CUDA tensor")
-        _check_same_device(signature, lower_columns=lower_columns)
-    desc.n_lower_columns = lower_columns.numel()
-    # a non-null marker is enough for the shape queries; an empty list still selects the projected layout
-    desc.lower_columns = (lower_columns.data_ptr() if not fake and lower_columns.numel() > 0 else 1)
+            desc.top_words = 1 if encoded_words.numel() > 0 else None  # non-null marker, never read
     return desc
 
 
@@ -247,236 +118,6 @@ def _row_width(d: int, depth: int, alt: bool, level_sizes: Sequence[int]) -> int
     if alt:
         return int(sum(int(s) for s in level_sizes[1: depth + 1]))
     return int(sum(d ** k for k in range(1, depth + 1)))
-
-
-# --------------------------------------------------------------------------------------
-# CUDA implementations
-# --------------------------------------------------------------------------------------
-
-def _compute_signature_cuda(path_in, depth, alternative_projection, encoded_words, level_sizes, use_windows,
-                            windows):
-    lib = _load.ensure_loaded()
-    path = path_in.contiguous()
-    desc, keep = _sig_desc(path, depth, alternative_projection, encoded_words, level_sizes, use_windows, windows)
-    D = _row_width(desc.d, desc.depth, bool(alternative_projection), level_sizes)
-    shape = (desc.B, desc.W, D) if use_windows else (desc.B, D)
-    out = torch.empty(shape, dtype=path.dtype, device=path.device)
-    if out.numel() == 0:  # no paths, no windows or no requested words: nothing to launch
-        return out
-    with torch.cuda.device(path.device):
-        rc = lib.psig_sig_forward(ctypes.byref(desc), _ptr(path), _ptr(out), _stream_ptr(path.device))
-    _load.check(rc, "compute_signature")
-    del keep
-    return out
-
-
-def _signature_backward_cuda(path_in, signature_in, grad_signature_in, depth, alternative_projection,
-                             encoded_words, level_sizes, use_windows, windows):
-    lib = _load.ensure_loaded()
-    if not signature_in.is_cuda:
-        raise RuntimeError("signature must be CUDA")
-    if not grad_signature_in.is_cuda:
-        raise RuntimeError("grad_signature must be CUDA")
-    if signature_in.dtype != path_in.dtype:
-        raise RuntimeError("signature must have same dtype as path")
-    if grad_signature_in.dtype != path_in.dtype:
-        raise RuntimeError("grad_signature must have same dtype as path")
-    if signature_in.shape != grad_signature_in.shape:
-        raise RuntimeError("grad_signature must match signature shape")
-    _check_same_device(path_in, signature=signature_in, grad_signature=grad_signature_in)
-    path = path_in.contiguous()
-    sig = signature_in.contiguous()
-    grad = grad_signature_in.contiguous()
-    desc, keep = _sig_desc(path, depth, alternative_projection, encoded_words, level_sizes, use_windows, windows)
-    D = _row_width(desc.d, desc.depth, bool(alternative_projection), level_sizes)
-    expect = (desc.B, desc.W, D) if use_windows else (desc.B, D)
-    if tuple(sig.shape) != expect:
-        if use_windows and sig.dim() == 3 and sig.size(1) != desc.W:
-            raise RuntimeError("windows.size(0) must match signature num_windows")
-        raise RuntimeError("signature must be [B,S] or [B,W,S]")
-    if sig.numel() == 0:  # an empty signature carries no gradient
-        return torch.zeros_like(path)
-    grad_path = torch.empty_like(path)
-    with torch.cuda.device(path.device):
-        ws_bytes = lib.psig_sig_backward_workspace(ctypes.byref(desc))
-        _load.check(ws_bytes, "signature_backward")
-        ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=path.device)
-        rc = lib.psig_sig_backward(ctypes.byref(desc), _ptr(path), _ptr(sig), _ptr(grad), _ptr(grad_path),
-                                   _ptr(ws), int(ws_bytes), _stream_ptr(path.device))
-    _load.check(rc, "signature_backward")
-    del keep
-    return grad_path
-
-
-def _sig_to_logsig_cuda(signature_in, depth, d, alternative_projection, encoded_words, level_sizes):
-    lib = _load.ensure_loaded()
-    if not signature_in.is_cuda:
-        raise RuntimeError("signature must be CUDA")
-    sig = signature_in.contiguous()
-    desc = _log_desc(sig, depth, d, alternative_projection, encoded_words, level_sizes)
-    with torch.cuda.device(sig.device):
-        S = lib.psig_logsig_size(ctypes.byref(desc))
-        _load.check(S, "sig_to_logsig")
-        if S != sig.size(-1):
-            raise RuntimeError(f"signature width {sig.size(-1)} does not match the layout width {S}")
-        logsig = torch.empty_like(sig)
-        per_row = lib.psig_logsig_cache_size(ctypes.byref(desc))
-        _load.check(per_row, "sig_to_logsig")
-        cache = torch.empty(sig.shape[:-1] + (int(per_row),), dtype=sig.dtype, device=sig.device)
-        rc = lib.psig_logsig_forward(ctypes.byref(desc), _ptr(sig), _ptr(logsig), _ptr(cache),
-                                     _stream_ptr(sig.device))
-    _load.check(rc, "sig_to_logsig")
-    return logsig, cache
-
-
-def _logsig_backward_cuda(signature_in, P_in, grad_logsig_in, depth, alternative_projection, encoded_words,
-                          level_sizes):
-    lib = _load.ensure_loaded()
-    if not signature_in.is_cuda:
-        raise RuntimeError("sig must be CUDA")
-    if not P_in.is_cuda:
-        raise RuntimeError("P must be CUDA")
-    if not grad_logsig_in.is_cuda:
-        raise RuntimeError("grad_logsig must be CUDA")
-    if P_in.dtype != signature_in.dtype:
-        raise RuntimeError("P must have same dtype as sig")
-    if grad_logsig_in.dtype != signature_in.dtype:
-        raise RuntimeError("grad_logsig must have same dtype as sig")
-    if grad_logsig_in.shape != signature_in.shape:
-        raise RuntimeError("grad_logsig must match sig shape")
-    _check_same_device(signature_in, P=P_in, grad_logsig=grad_logsig_in)
-    if len(level_sizes) <= int(depth):
-        raise RuntimeError("level_sizes must have entries up to depth")
-    d = int(level_sizes[1])  # the channel count travels in level_sizes[1], as in the reference
-    if d < 1:
-        raise RuntimeError("level_sizes[1] must be >= 1 (infers path_dim)")
-    sig = signature_in.contiguous()
-    cache = P_in.contiguous()
-    grad = grad_logsig_in.contiguous()
-    desc = _log_desc(sig, depth, d, alternative_projection, encoded_words, level_sizes)
-    # The cache tells which kernel family produced it: the table of powers (S*depth per row) belongs to
-    # the global-memory kernels, an empty one to the row-in-shared-memory kernels.
-    if tuple(cache.shape[:-1]) != tuple(sig.shape[:-1]) or cache.size(-1) not in (0, sig.size(-1) * int(depth)):
-        raise RuntimeError("P must be [B,(W),S*depth] (or [B,(W),0] as returned by sig_to_logsig)")
-    desc.algo = _load.ALGO_GENERIC if cache.size(-1) > 0 else _load.ALGO_AUTO
-    if lib.psig_logsig_cache_size(ctypes.byref(desc)) != cache.size(-1):
-        raise RuntimeError("P does not belong to a sig_to_logsig call with these arguments")
-    grad_sig = torch.empty_like(sig)
-    with torch.cuda.device(sig.device):
-        ws_bytes = lib.psig_logsig_backward_workspace(ctypes.byref(desc))
-        _load.check(ws_bytes, "logsig_backward")
-        ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=sig.device)
-        rc = lib.psig_logsig_backward(ctypes.byref(desc), _ptr(sig), _ptr(cache), _ptr(grad), _ptr(grad_sig),
-                                      _ptr(ws), int(ws_bytes), _stream_ptr(sig.device))
-    _load.check(rc, "logsig_backward")
-    return grad_sig
-
-
-def _logsig_projected_cuda(signature_in, depth, d, top_words, level_sizes, lower_columns):
-    lib = _load.ensure_loaded()
-    if not signature_in.is_cuda:
-        raise RuntimeError("signature must be CUDA")
-    sig = signature_in.contiguous()
-    desc = _projected_log_desc(sig, depth, d, top_words, level_sizes, lower_columns)
-    with torch.cuda.device(sig.device):
-        S = lib.psig_logsig_size(ctypes.byref(desc))
-        _load.check(S, "logsig_projected")
-        if S != sig.size(-1):
-            raise RuntimeError(f"signature width {sig.size(-1)} does not match the layout width {S}")
-        width = lib.psig_logsig_out_size(ctypes.byref(desc))
-        _load.check(width, "logsig_projected")
-        out = torch.empty(sig.shape[:-1] + (int(width),), dtype=sig.dtype, device=sig.device)
-        if out.numel() == 0:
-            return out
-        rc = lib.psig_logsig_forward(ctypes.byref(desc), _ptr(sig), _ptr(out), None, _stream_ptr(sig.device))
-    _load.check(rc, "logsig_projected")
-    return out
-
-
-def _logsig_projected_backward_cuda(signature_in, grad_out, depth, d, top_words, level_sizes, lower_columns):
-    lib = _load.ensure_loaded()
-    if not signature_in.is_cuda or not grad_out.is_cuda:
-        raise RuntimeError("signature and grad_out must be CUDA")
-    if grad_out.dtype != signature_in.dtype:
-        raise RuntimeError("grad_out must have same dtype as signature")
-    _check_same_device(signature_in, grad_out=grad_out)
-    sig = signature_in.contiguous()
-    grad = grad_out.contiguous()
-    desc = _projected_log_desc(sig, depth, d, top_words, level_sizes, lower_columns)
-    with torch.cuda.device(sig.device):
-        width = lib.psig_logsig_out_size(ctypes.byref(desc))
-        _load.check(width, "logsig_projected_backward")
-        if tuple(grad.shape) != tuple(sig.shape[:-1]) + (int(width),):
-            raise RuntimeError("grad_out must be [B,(W),n_lower_columns + top_size]")
-        grad_sig = torch.empty_like(sig)
-        if grad_sig.numel() == 0:
-            return grad_sig
-        rc = lib.psig_logsig_backward(ctypes.byref(desc), _ptr(sig), None, _ptr(grad), _ptr(grad_sig), None, 0,
-                                      _stream_ptr(sig.device))
-    _load.check(rc, "logsig_projected_backward")
-    return grad_sig
-
-
-def _chen_desc(sig_a: Tensor, sig_b: Tensor, depth: int, d: int) -> _load.ChenDesc:
-    depth, d = int(depth), int(d)
-    if not sig_a.is_cuda or not sig_b.is_cuda:
-        raise RuntimeError("signatures must be CUDA")
-    if not (1 <= depth <= _load.MAX_DEPTH):
-        raise RuntimeError("depth must be in [1,12]")
-    if d < 1:
-        raise RuntimeError("d must be >= 1")
-    if sig_a.dtype != sig_b.dtype:
-        raise RuntimeError("signatures must have the same dtype")
-    _check_same_device(sig_a, sig_b=sig_b)
-    if sig_a.shape != sig_b.shape or sig_a.dim() < 1:
-        raise RuntimeError("signatures must have the same shape (..., D)")
-    D = sum(d ** k for k in range(1, depth + 1))
-    if sig_a.size(-1) != D:
-        raise RuntimeError(f"signature width {sig_a.size(-1)} is not the dense width {D} for d={d}, depth={depth}")
-    desc = _load.ChenDesc()
-    desc.dtype = _dtype_id(sig_a)
-    desc.d, desc.depth = d, depth
-    desc.rows = sig_a.numel() // D
-    return desc
-
-
-def _chen_product_cuda(sig_a, sig_b, depth, d):
-    lib = _load.ensure_loaded()
-    desc = _chen_desc(sig_a, sig_b, depth, d)
-    a, b = sig_a.contiguous(), sig_b.contiguous()
-    out = torch.empty_like(a)
-    if out.numel() == 0:
-        return out
-    with torch.cuda.device(a.device):
-        rc = lib.psig_chen_forward(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(out), _stream_ptr(a.device))
-    _load.check(rc, "chen_product")
-    return out
-
-
-def _chen_product_backward_cuda(sig_a, sig_b, grad_out, depth, d):
-    lib = _load.ensure_loaded()
-    desc = _chen_desc(sig_a, sig_b, depth, d)
-    if not grad_out.is_cuda:
-        raise RuntimeError("grad_out must be CUDA")
-    if grad_out.dtype != sig_a.dtype or grad_out.shape != sig_a.shape:
-        raise RuntimeError("grad_out must match the signatures in dtype and shape")
-    _check_same_device(sig_a, grad_out=grad_out)
-    a, b, g = sig_a.contiguous(), sig_b.contiguous(), grad_out.contiguous()
-    ga, gb = torch.empty_like(a), torch.empty_like(a)
-    if ga.numel() == 0:
-        return ga, gb
-    with torch.cuda.device(a.device):
-        rc = lib.psig_chen_backward(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(g), _ptr(ga), _ptr(gb),
-                                    _stream_ptr(a.device))
-    _load.check(rc, "chen_product_backward")
-    return ga, gb
-
-
-def _no_cpu(name):
-    def impl(*args, **kwargs):
-        raise NotImplementedError(
-            f"pathsig_b200::{name} has a CUDA (sm_100a) implementation only; move the inputs to a CUDA device.")
-    return impl
 
 
 # --------------------------------------------------------------------------------------
@@ -545,7 +186,7 @@ def _fake_sig_to_logsig(signature, depth, d, alternative_projection, encoded_wor
     torch._check(signature.dim() in (2, 3), lambda: "signature must be 2D or 3D")
     if alternative_projection:
         _fake_check_projection(encoded_words, level_sizes, depth)
-    desc = _log_desc(signature, depth, d, alternative_projection, encoded_words, level_sizes, fake=True)
+    desc = _log_desc_for_shapes(signature, depth, d, alternative_projection, encoded_words, level_sizes)
     per_row = _load.ensure_loaded().psig_logsig_cache_size(ctypes.byref(desc))
     _load.check(per_row, "sig_to_logsig")
     cache = signature.new_empty(tuple(signature.shape[:-1]) + (int(per_row),))
@@ -599,30 +240,47 @@ def _fake_chen_product_backward(sig_a, sig_b, grad_out, depth, d):
 # registration
 # --------------------------------------------------------------------------------------
 
-_IMPLS = {
-    "compute_signature": (_compute_signature_cuda, _fake_compute_signature),
-    "signature_backward": (_signature_backward_cuda, _fake_signature_backward),
-    "sig_to_logsig": (_sig_to_logsig_cuda, _fake_sig_to_logsig),
-    "logsig_backward": (_logsig_backward_cuda, _fake_logsig_backward),
-    "logsig_projected": (_logsig_projected_cuda, _fake_logsig_projected),
-    "logsig_projected_backward": (_logsig_projected_backward_cuda, _fake_logsig_projected_backward),
-    "chen_product": (_chen_product_cuda, _fake_chen_product),
-    "chen_product_backward": (_chen_product_backward_cuda, _fake_chen_product_backward),
+_FAKES = {
+    "compute_signature": _fake_compute_signature,
+    "signature_backward": _fake_signature_backward,
+    "sig_to_logsig": _fake_sig_to_logsig,
+    "logsig_backward": _fake_logsig_backward,
+    "logsig_projected": _fake_logsig_projected,
+    "logsig_projected_backward": _fake_logsig_projected_backward,
+    "chen_product": _fake_chen_product,
+    "chen_product_backward": _fake_chen_product_backward,
 }
-_libraries = {}  # namespace -> torch.library.Library (kept alive for the life of the process)
+_libraries = {}  # namespace -> torch.library.Library or True (kept alive for the life of the process)
+
+
+def _forward_to_compiled(name):
+    compiled = getattr(getattr(torch.ops, NAMESPACE), name).default
+
+    def impl(*args):
+        return compiled(*args)
+    return impl
 
 
 def register_namespace(ns: str) -> None:
-    """Define and implement the four operators under ``torch.ops.<ns>``."""
+    """Fake implementations and autograd formulas of the operators under ``torch.ops.<ns>``.
+
+    For ``pathsig_b200`` the operators themselves (schemas and CUDA implementations) come from the
+    compiled library ``libpathsig_b200_torch.so``; any other namespace (``pathsig``, for code written
+    against the reference) is defined here and forwards to them.
+    """
     if ns in _libraries:
         return
-    lib = torch.library.Library(ns, "FRAGMENT")
-    for name, schema in _SCHEMAS.items():
-        lib.define(name + schema, tags=(torch.Tag.pt2_compliant_tag,))
-        cuda_impl, fake_impl = _IMPLS[name]
-        lib.impl(name, cuda_impl, "CUDA")
-        lib.impl(name, _no_cpu(name), "CPU")
-        torch.library.register_fake(f"{ns}::{name}", fake_impl, lib=lib)
+    lib = None
+    if ns == NAMESPACE:
+        _load.ensure_binding_loaded()
+        for name, fake_impl in _FAKES.items():
+            torch.library.register_fake(f"{ns}::{name}", fake_impl)
+    else:
+        lib = torch.library.Library(ns, "FRAGMENT")
+        for name, schema in _SCHEMAS.items():
+            lib.define(name + schema, tags=(torch.Tag.pt2_compliant_tag,))
+            lib.impl(name, _forward_to_compiled(name), "CUDA")
+            torch.library.register_fake(f"{ns}::{name}", _FAKES[name], lib=lib)
 
     def setup_sig(ctx, inputs, output):
         path, depth, alt, encoded_words, level_sizes, use_windows, windows = inputs
@@ -710,7 +368,7 @@ def register_namespace(ns: str) -> None:
     torch.library.register_autograd(f"{ns}::compute_signature", backward_sig, setup_context=setup_sig, lib=lib)
     torch.library.register_autograd(f"{ns}::sig_to_logsig", backward_log, setup_context=setup_log, lib=lib)
     torch.library.register_autograd(f"{ns}::logsig_projected", backward_logproj, setup_context=setup_logproj, lib=lib)
-    _libraries[ns] = lib
+    _libraries[ns] = lib if lib is not None else True
 
 
 register_namespace(NAMESPACE)

@@ -75,3 +75,36 @@ def test_gather_and_its_backward_on_two_ranks(batch):
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(world))
     assert results == {0: True, 1: True}
+
+
+def _worker_rank_losses(rank, world, port, batch, q):
+    """Each rank differentiates its OWN loss of the gathered tensor: the gradient of a rank's rows is the
+    sum over all ranks' losses, which needs reduce_grads=True."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(batch, 3, generator=g, dtype=torch.float64)
+        weights = [torch.randn(batch, 3, generator=g, dtype=torch.float64) for _ in range(world)]
+        mine = shard_batch(x).clone().requires_grad_(True)
+        lo, hi = shard_bounds(batch, rank, world)
+        full = gather_batch(mine * 2.0, reduce_grads=True)
+        (full * weights[rank]).sum().backward()                      # this rank's loss
+        expect = 2.0 * sum(weights)[lo:hi]                            # d(sum of all ranks' losses) / d(mine)
+        q.put((rank, bool(torch.allclose(mine.grad, expect))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("batch", [8, 7])
+def test_gather_with_rank_dependent_losses_reduces_the_gradients(batch):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_rank_losses, args=(r, world, port, batch, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert dict(q.get(timeout=10) for _ in range(world)) == {0: True, 1: True}

@@ -194,16 +194,26 @@ def test_install_as_pathsig_aliases_the_package():
     assert torch.ops.pathsig.compute_signature is not None
 
 
-def test_operands_on_another_device_are_refused_before_any_launch():
-    """A tensor operand on a different device than the path must raise on the host: the dispatcher
-    does not check devices for operators registered from Python, and the kernels would otherwise
-    receive a pointer into another GPU's memory."""
-    from pathsig_b200 import ops
-    path = torch.empty(2, 4, 3, device="meta")
-    other = torch.empty(5, dtype=torch.int64)  # lives on the CPU: a different device
-    with pytest.raises(RuntimeError, match="encoded_words must be on the same device"):
-        ops._check_same_device(path, encoded_words=other)
-    ops._check_same_device(path, windows=torch.empty((0, 2), dtype=torch.int32, device="meta"))
+def test_operators_are_registered_by_the_compiled_library():
+    """The eight operators come from libpathsig_b200_torch.so (TORCH_LIBRARY + TORCH_LIBRARY_IMPL for the
+    CUDA key, like the reference's bindings.cpp and launchers); Python adds the fake implementations and
+    the autograd formulas.  There is no CPU kernel: CPU tensors are refused by the dispatcher."""
+    from pathsig_b200 import _load, ops
+    binding = _load.ensure_binding_loaded()
+    assert binding.psig_torch_get_algorithm() == _load.ALGO_AUTO
+    for name, schema in ops._SCHEMAS.items():
+        op = getattr(torch.ops.pathsig_b200, name).default
+        assert str(op._schema) == f"pathsig_b200::{name}{schema}"
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"pathsig_b200::{name}", "CUDA")
+        assert not torch._C._dispatch_has_kernel_for_dispatch_key(f"pathsig_b200::{name}", "CPU")
+        assert torch.Tag.pt2_compliant_tag in op.tags
+    ops.set_algorithm("generic")
+    try:
+        assert binding.psig_torch_get_algorithm() == _load.ALGO_GENERIC
+    finally:
+        ops.set_algorithm("auto")
+    with pytest.raises(NotImplementedError):
+        ops.chen_product(torch.zeros(2, 6), torch.zeros(2, 6), 2, 2)
 
 
 def test_word_codes_are_range_checked_on_the_host():
