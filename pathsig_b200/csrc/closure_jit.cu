@@ -25,6 +25,10 @@
 #include "common.cuh"
 
 #include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cerrno>
 
 #include <algorithm>
 #include <cstdio>
@@ -888,10 +892,58 @@ std::string arch_option(int device)
     return a;
 }
 
+// Directory of compiled kernels kept across processes: $PATHSIG_B200_CACHE_DIR, else $XDG_CACHE_HOME/pathsig_b200,
+// else ~/.cache/pathsig_b200; "" (the variable set to an empty string, or no home directory) turns the cache off.
+std::string cache_dir()
+{
+    if (const char *e = getenv("PATHSIG_B200_CACHE_DIR")) return e;
+    if (const char *x = getenv("XDG_CACHE_HOME")) { if (*x) return std::string(x) + "/pathsig_b200"; }
+    if (const char *h = getenv("HOME")) { if (*h) return std::string(h) + "/.cache/pathsig_b200"; }
+    return "";
+}
+
+long long spill_bytes(const std::string &log);
+
+// mkdir -p
+bool make_dirs(const std::string &dir)
+{
+    for (size_t pos = 1; pos <= dir.size(); ++pos) {
+        if (pos != dir.size() && dir[pos] != '/') continue;
+        const std::string part = dir.substr(0, pos);
+        if (mkdir(part.c_str(), 0755) != 0 && errno != EEXIST) return false;
+    }
+    return true;
+}
+
+unsigned long long fnv1a(const std::string &s, unsigned long long h = 1469598103934665603ull)
+{
+    for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
 // Compiles `text` to a cubin for `arch` ("--gpu-architecture=sm_100a"); empty result on failure (log filled).
+// A cubin compiled before for the same text and options is read back from the cache directory (the file
+// name is a hash of both, and the file starts with the text's length and a second hash as a check).
 std::vector<char> compile(const std::string &text, const std::string &arch, std::string *log)
 {
     std::vector<char> cubin;
+    const std::string dir = cache_dir();
+    const unsigned long long key = fnv1a(arch, fnv1a(text)), check_hash = fnv1a(text, 88172645463325252ull);
+    char name[64];
+    snprintf(name, sizeof(name), "/closure_%016llx.cubin", key);
+    const std::string file = dir.empty() ? "" : dir + name;
+    if (!file.empty()) {
+        if (FILE *f = fopen(file.c_str(), "rb")) {
+            unsigned long long head[3] = {0, 0, 0};
+            if (fread(head, sizeof(head), 1, f) == 1 && head[0] == text.size() && head[1] == check_hash && head[2] > 0 &&
+                head[2] < (1ull << 31)) {
+                cubin.resize((size_t)head[2]);
+                if (fread(cubin.data(), 1, cubin.size(), f) != cubin.size()) cubin.clear();
+            }
+            fclose(f);
+            if (!cubin.empty()) { *log = "ptxas info    : read from " + file + "\n"; return cubin; }
+        }
+    }
     const Nvrtc &rt = nvrtc();
     if (!rt.ok) { *log = "NVRTC not available"; return cubin; }
     nvrtcProgram prog = nullptr;
@@ -912,6 +964,18 @@ std::vector<char> compile(const std::string &text, const std::string &arch, std:
         }
     }
     rt.DestroyProgram(&prog);
+    // keep it for the next process, unless this version spilled (its caller will replace it)
+    if (!cubin.empty() && !file.empty() && spill_bytes(*log) == 0) {
+        if (make_dirs(dir)) {
+            const std::string tmp = file + ".tmp" + std::to_string((long long)getpid());
+            if (FILE *f = fopen(tmp.c_str(), "wb")) {
+                const unsigned long long head[3] = {text.size(), check_hash, cubin.size()};
+                const bool ok = fwrite(head, sizeof(head), 1, f) == 1 && fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+                fclose(f);
+                if (!ok || rename(tmp.c_str(), file.c_str()) != 0) remove(tmp.c_str());
+            }
+        }
+    }
     return cubin;
 }
 

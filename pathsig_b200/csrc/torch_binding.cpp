@@ -392,6 +392,7 @@ extern "C" int psig_torch_get_algorithm(void) { return g_algo.load(); }
 TORCH_LIBRARY(pathsig_b200, m)
 {
     const auto tag = at::Tag::pt2_compliant_tag;
+    m.set_python_module("pathsig_b200.ops");  // where the fake implementations and autograd formulas live
     m.def("compute_signature(Tensor path_in, int depth, bool alternative_projection, Tensor encoded_words, "
           "int[] level_sizes, bool use_windows, Tensor windows) -> Tensor", {tag});
     m.def("signature_backward(Tensor path_in, Tensor signature_in, Tensor grad_signature_in, int depth, "

@@ -275,3 +275,25 @@ def test_closure_generator_counts_and_compiles_for_sm100a():
     # a word listed twice has no unique column: the plan is refused
     desc, keep = _closure_desc([1, 1], [0, 3, 2, 0], 3, 3)
     assert lib.psig_closure_source(ctypes.byref(desc), 2, None, 0, stats) < 0
+
+
+def test_compiled_closure_kernels_are_kept_on_disk(tmp_path, monkeypatch):
+    """A cubin compiled once is read back by the next compilation of the same source and options
+    (another process, typically) from the cache directory."""
+    import ctypes
+
+    from pathsig_b200 import _load
+    lib = _load.ensure_loaded()
+    monkeypatch.setenv("PATHSIG_B200_CACHE_DIR", str(tmp_path / "kernels"))
+    small = ps.projections.words([(0, 1), (1, 1, 0)], 3, 2, full_levels=(1,), device="cpu")
+    desc, keep = _closure_desc(small.encoded_words.tolist(), small.level_sizes, 2, 3)
+    stats = (ctypes.c_int64 * 5)()
+    n = lib.psig_closure_source(ctypes.byref(desc), 1, None, 0, stats)
+    buf = ctypes.create_string_buffer(n + 1)
+    lib.psig_closure_source(ctypes.byref(desc), 1, buf, n + 1, stats)
+    log = ctypes.create_string_buffer(1 << 14)
+    assert lib.psig_closure_compile(buf.value, b"sm_100a", log, 1 << 14) == 0
+    assert b"read from" not in log.value
+    assert len(list((tmp_path / "kernels").glob("closure_*.cubin"))) == 2     # forward and backward pass
+    assert lib.psig_closure_compile(buf.value, b"sm_100a", log, 1 << 14) == 0
+    assert log.value.count(b"read from") == 2
