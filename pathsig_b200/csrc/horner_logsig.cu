@@ -641,9 +641,6 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
     // under half of the largest supported footprint
     p.stage_top = (p.depth >= 2 &&
                    sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top_dense) <= kHornerMaxSmem / 2) ? 1u : 0u;
-    // A sparse list of top words (a Lyndon projection keeps a sixth of the degree) is cheaper to scatter word by
-    // word (2 (N-1) shared-memory atomics each) than to run through the dense gathers (2 (N-1) d^N multiply-adds).
-    if (p.top_words != nullptr && 3ull * p.top < p.top_dense) p.stage_top = 0u;
     const size_t smem = backward_smem<T>(p);
     auto launch = [&](auto kernel) {
         if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
