@@ -219,7 +219,7 @@ template <typename T, int NMAX, class F>
 __device__ __forceinline__ void for_words_below_top(const HornerPlan &p, int M, const T *xs, const T *ts, F &&emit)
 {
     if (M < 2) return;
-    for (unsigned i = threadIdx.x; i < p.off[M]; i += kHornerBlock) {  // parents: degrees 1..M-1
+    for (unsigned i = threadIdx.x; i < p.off[M]; i += blockDim.x) {  // parents: degrees 1..M-1
         const int m = degree_at(p, i, M - 1);
         const unsigned u = i - p.off[m];
         const unsigned first = p.off[m + 1] + u * (unsigned)p.d;
@@ -238,7 +238,7 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
     for (int k = N - 1; k >= 1; --k) {
         const T c = T(1) / T(k + 1);  // degree-0 term of T_{k+1}
         T *kept = keep ? keep + p.t_off[k] : nullptr;
-        for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) {  // degree 1: no split
+        for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += blockDim.x) {  // degree 1: no split
             const T v = -xs[i] * c;
             nxt[i] = v;
             if (kept) kept[i] = v;
@@ -267,20 +267,20 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
         const T *s = sig + row * p.width;
         T *l = logsig + row * p.out_width;
         __syncthreads();  // the previous row's readers are done with the buffers
-        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) xs[i] = s[i];
+        for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) xs[i] = s[i];
         __syncthreads();
         const T *t1 = build_t<T, NMAX>(p, xs, ta, tb, nullptr);
         // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
         if (p.low_cols != nullptr) {
             // projected output: only the requested words below the top degree, each from its own splits
-            for (unsigned i = threadIdx.x; i < p.n_low; i += kHornerBlock) {
+            for (unsigned i = threadIdx.x; i < p.n_low; i += blockDim.x) {
                 const unsigned pos = (unsigned)p.low_cols[i];
                 const int n = degree_at(p, pos, N - 1);
                 l[i] = xs[pos] + (n >= 2 ? split_sum(p, xs, t1, n, pos - p.off[n]) : T(0));
             }
         } else {
             if (N >= 2)
-                for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += kHornerBlock) l[i] = xs[i];
+                for (unsigned i = threadIdx.x; i < (unsigned)p.d; i += blockDim.x) l[i] = xs[i];
             for_words_below_top<T, NMAX>(p, N - 1, xs, t1, [&](unsigned pos, T acc) { l[pos] = xs[pos] + acc; });
         }
         if (p.top_words == nullptr && N >= 2) {
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
             if (quads) {
                 // a thread takes one quad of children; neighbouring threads take neighbouring quads
                 const unsigned per_parent = (unsigned)p.d / 4u, items = parents * per_parent;
-                for (unsigned it = threadIdx.x; it < items; it += kHornerBlock) {
+                for (unsigned it = threadIdx.x; it < items; it += blockDim.x) {
                     const unsigned u = it / per_parent, a = 4u * (it - u * per_parent);
                     T acc[4];
                     PSIG_QUAD(N, p, xs, t1, u, a, acc)
@@ -306,14 +306,14 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
                     *reinterpret_cast<Quad<T> *>(l + p.out_lower + pos) = o;
                 }
             } else {
-                for (unsigned u = threadIdx.x; u < parents; u += kHornerBlock) {
+                for (unsigned u = threadIdx.x; u < parents; u += blockDim.x) {
                     const T *srun = s + p.lower + (size_t)u * p.d;
                     T *lrun = l + p.out_lower + (size_t)u * p.d;
                     PSIG_CHILDREN(N, p, xs, t1, u, [&](unsigned a, T acc) { lrun[a] = srun[a] + acc; })
                 }
             }
         } else {
-            for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+            for (unsigned i = threadIdx.x; i < p.top; i += blockDim.x) {
                 const unsigned code = p.top_words ? (unsigned)p.top_words[i] : i;
                 l[p.out_lower + i] = s[p.lower + i] + split_sum(p, xs, t1, N, code);
             }
@@ -345,7 +345,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
     const unsigned thread_words = words - warp_words;
     const unsigned total = warp_threads + 2u * thread_words;
     const unsigned span = (total + 31u) / 32u * 32u;
-    for (unsigned t = threadIdx.x; t < span; t += kHornerBlock) {
+    for (unsigned t = threadIdx.x; t < span; t += blockDim.x) {
         const bool team = t < warp_threads;
         unsigned word, lane, stride;
         int side;
@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
         const T *gtop = p.stage_top ? gts : gtop_global;  // re-read N-1 times by each side of the adjoint
         T *out = gsig + row * p.width;
         __syncthreads();
-        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) {
+        for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) {
             xs[i] = s[i];
             const T gi = p.low_cols != nullptr ? T(0) : g[i];
             gl[i] = gi;
@@ -429,18 +429,18 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
             // projected gradient: spread it over the dense image of the lower degrees (a word may be
             // requested twice), then start gx from it
             __syncthreads();
-            for (unsigned i = threadIdx.x; i < p.n_low; i += kHornerBlock) atomicAdd(&gl[(unsigned)p.low_cols[i]], g[i]);
+            for (unsigned i = threadIdx.x; i < p.n_low; i += blockDim.x) atomicAdd(&gl[(unsigned)p.low_cols[i]], g[i]);
             __syncthreads();
-            for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) gx[i] = gl[i];
+            for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) gx[i] = gl[i];
         }
         // the top degree of x enters only through that same term
         if (p.stage_top && p.top_words != nullptr) {
             // a projected top degree is scattered into a dense image (zeros elsewhere), after which it
             // goes through the same gathers as a dense one
-            for (unsigned i = threadIdx.x; i < p.top_dense; i += kHornerBlock) gts[i] = T(0);
+            for (unsigned i = threadIdx.x; i < p.top_dense; i += blockDim.x) gts[i] = T(0);
             __syncthreads();
         }
-        for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+        for (unsigned i = threadIdx.x; i < p.top; i += blockDim.x) {
             const T gi = gtop_global[i];
             out[p.lower + i] = gi;
             if (p.stage_top) {
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
         __syncthreads();
         build_t<T, NMAX>(p, xs, ga, gb, tk);  // ends with a barrier
         const T *t1 = tk + p.t_off[1];
-        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) ga[i] = T(0);
+        for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) ga[i] = T(0);
         __syncthreads();
 
         // ---- log S = x (x) T_1: words below the top degree ----
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
                     return w;
                 }();
                 const unsigned span = ((32u * long_words + (p.lower - long_words)) + 31u) / 32u * 32u;
-                for (unsigned t = threadIdx.x; t < span; t += kHornerBlock) {
+                for (unsigned t = threadIdx.x; t < span; t += blockDim.x) {
                     const bool team = t < 32u * long_words;
                     const unsigned word = team ? (t >> 5) : long_words + (t - 32u * long_words);
                     const unsigned lane = team ? (t & 31u) : 0u, stride = team ? 32u : 1u;
@@ -496,8 +496,8 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
                     const unsigned pieces = (du + 63u) / 64u;
                     const unsigned items = dq * pieces;
                     // this degree's items are dealt to the threads after those of the degrees before it
-                    for (unsigned it = (threadIdx.x + kHornerBlock - items_before % kHornerBlock) % kHornerBlock;
-                         it < items; it += kHornerBlock) {
+                    for (unsigned it = (threadIdx.x + blockDim.x - items_before % blockDim.x) % blockDim.x;
+                         it < items; it += blockDim.x) {
                         const unsigned piece = it / dq, v = it - piece * dq;
                         const unsigned u0 = piece * 64u, u1 = min(du, u0 + 64u);
                         const T *xrun = xs + p.off[N - q];
@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
                 }
             } else {
                 // projected: each listed word scatters its N-1 splits
-                for (unsigned i = threadIdx.x; i < p.top; i += kHornerBlock) {
+                for (unsigned i = threadIdx.x; i < p.top; i += blockDim.x) {
                     const unsigned code = (unsigned)p.top_words[i];
                     const T gw = gtop[i];
                     unsigned q = code;
@@ -530,14 +530,14 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
         for (int k = 1; k <= N - 1; ++k) {
             const int M = N - k;
             const T c = T(1) / T(k + 1);
-            for (unsigned i = threadIdx.x; i < p.off[M + 1]; i += kHornerBlock) gx[i] -= c * gk[i];
-            for (unsigned i = threadIdx.x; i < p.off[M]; i += kHornerBlock) gn[i] = T(0);
+            for (unsigned i = threadIdx.x; i < p.off[M + 1]; i += blockDim.x) gx[i] -= c * gk[i];
+            for (unsigned i = threadIdx.x; i < p.off[M]; i += blockDim.x) gn[i] = T(0);
             __syncthreads();
             if (k < N - 1) adjoint_in_smem<T>(p, M, xs, tk + p.t_off[k + 1], gk, T(-1), gx, gn, true);
             __syncthreads();
             T *tmp = gk; gk = gn; gn = tmp;
         }
-        for (unsigned i = threadIdx.x; i < p.lower; i += kHornerBlock) out[i] = gx[i];
+        for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) out[i] = gx[i];
     }
 }
 
@@ -598,6 +598,12 @@ template <typename T> size_t backward_smem(const HornerPlan &p)
     return sizeof(T) * (5 * (size_t)p.lower + p.t_total + (p.stage_top ? (size_t)p.top_dense : 0));
 }
 
+// Threads per row (= per block).  The kernels stride by the launched block size; narrower blocks were
+// measured (config 4 and a dense (8,4) row): 128 threads gain 15 % forward and lose 35 % backward, 64 and
+// 32 threads lose up to 3.5x -- a row's phases are parallel inside the row, and rows in flight are limited
+// by shared memory, not by threads.
+unsigned horner_block(long long) { return kHornerBlock; }
+
 unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : (1 << 20)); }
 
 }  // namespace
@@ -621,7 +627,7 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
     auto launch = [&](auto kernel) {
         // rows in flight are limited by shared memory under the default L1 split
         if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, logsig);
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, logsig);
         return check_launch();
     };
     if (p.depth <= 4) return launch(logsig_forward_horner<T, 4>);
@@ -644,7 +650,7 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
     const size_t smem = backward_smem<T>(p);
     auto launch = [&](auto kernel) {
         if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), kHornerBlock, smem, stream>>>(p, sig, grad_logsig, grad_sig);
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, grad_logsig, grad_sig);
         return check_launch();
     };
     if (p.depth <= 4) return launch(logsig_backward_horner<T, 4>);
