@@ -37,6 +37,13 @@ template <typename T, int NMAX> constexpr int forward_blocks_per_sm()
 #define PSIG_HORNER_MINB_BWD 1
 #endif
 constexpr size_t kHornerMaxSmem = 160 * 1024;
+// Balance of the backward gathers: a word whose sum has at least kTeamTerms terms gets a warp (lanes stride the
+// sum), shorter sums get a thread; sums over the first factor are cut into pieces of kPieceTerms terms.  With a
+// warp only for sums of 96+ terms and pieces of 64, a few threads ran serial loops of 64-84 terms while the rest
+// of the block waited at the phase barrier.
+// Measured (config 4 at 1 024 rows / dense (8,4) at 15 616 rows): 96/64 0.117/0.772 ms, 48/32 0.111/0.620 ms,
+// 32/16 0.110/0.633 ms, 16/8 0.185/0.652 ms.
+constexpr unsigned kTeamTerms = 48, kPieceTerms = 32;
 
 // Division of a 32-bit unsigned number by the channel count, which is fixed for a launch: the
 // multiply-and-shift form of Granlund & Montgomery ("Division by invariant integers using
@@ -340,7 +347,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
     // degrees 1..mw get warps: their sums have off[M-m+1] terms
     unsigned warp_words = 0;
     for (int m = 1; m <= M - 1; ++m)
-        if (p.off[M - m + 1] >= 96u) warp_words = p.off[m + 1];
+        if (p.off[M - m + 1] >= kTeamTerms) warp_words = p.off[m + 1];
     const unsigned warp_threads = 64u * warp_words;
     const unsigned thread_words = words - warp_words;
     const unsigned total = warp_threads + 2u * thread_words;
@@ -464,7 +471,7 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
                 const unsigned long_words = [&] {
                     unsigned w = 0;
                     for (int m = 1; m <= N - 1; ++m)
-                        if (p.dpow[N - m] >= 64u) w = p.off[m + 1];
+                        if (p.dpow[N - m] >= kTeamTerms) w = p.off[m + 1];
                     return w;
                 }();
                 const unsigned span = ((32u * long_words + (p.lower - long_words)) + 31u) / 32u * 32u;
@@ -489,17 +496,17 @@ __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_bac
                     if (live && lane == 0u) gx[word] += acc;
                 }
                 // gT_1[v] += sum_u x(u) gtop[u.v]: neighbouring threads take neighbouring v (coalesced
-                // reads of the top degree); long sums over u are cut into pieces of at most 64 terms
+                // reads of the top degree); long sums over u are cut into pieces of at most kPieceTerms terms
                 unsigned items_before = 0;
                 for (int q = 1; q <= N - 1; ++q) {
                     const unsigned dq = p.dpow[q], du = p.dpow[N - q];
-                    const unsigned pieces = (du + 63u) / 64u;
+                    const unsigned pieces = (du + kPieceTerms - 1u) / kPieceTerms;
                     const unsigned items = dq * pieces;
                     // this degree's items are dealt to the threads after those of the degrees before it
                     for (unsigned it = (threadIdx.x + blockDim.x - items_before % blockDim.x) % blockDim.x;
                          it < items; it += blockDim.x) {
                         const unsigned piece = it / dq, v = it - piece * dq;
-                        const unsigned u0 = piece * 64u, u1 = min(du, u0 + 64u);
+                        const unsigned u0 = piece * kPieceTerms, u1 = min(du, u0 + kPieceTerms);
                         const T *xrun = xs + p.off[N - q];
                         T acc = T(0);
 #pragma unroll 4
