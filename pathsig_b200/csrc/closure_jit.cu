@@ -466,21 +466,24 @@ struct BinGen {
                 }
                 e.line(pad + "  }");
             }
+        // Unpaired siblings.  Their Horner values are b = S + s*x with the common s = bpar/(m-depth+1), so the
+        // adjoint of s is gathered over the siblings (g) and scaled once; the letter gradient takes a*s.
+        const std::string g = "g" + dn;
+        const bool gather = i < act.size() && !bpar.empty();
+        if (gather) e.line(pad + "  real " + g + " = (real)0;");
         for (; i < act.size(); ++i) {
             const int k = act[i];
             const std::string bp = "b" + dn + "p", p0 = "a" + dn + "p0", p1 = "a" + dn + "p1";
-            e.line(pad + "  { const real " + bp + " = fma(" + bs + ", " + xr(k) + ", " + S(k) + "); real " + p0 + " = (real)0, " + p1 + " = (real)0;");
-            bwd_siblings(e, x, kids[k], m, bp, p0, p1, indent + 4);
-            e.line(pad + "    " + p0 + " += " + p1 + ";");
+            e.line(pad + "  { const real " + bp + " = fma(" + bs + ", " + xr(k) + ", " + S(k) + "); real " + p0 + " = (real)0" +
+                   (packed ? ", " + p1 + " = (real)0;" : ";"));
+            bwd_siblings(e, x, kids[k], m, bp, p0, packed ? p1 : p0, indent + 4);
+            if (packed) e.line(pad + "    " + p0 + " += " + p1 + ";");
             e.line(pad + "    " + A(k) + " += " + p0 + ";");
-            e.line(pad + "    " + p0 + " *= " + rc + ";");
-            if (bpar.empty()) e.line(pad + "    " + lg(k) + " += " + p0 + ";");
-            else {
-                e.line(pad + "    " + ap0 + " = fma(" + p0 + ", " + xr(k) + ", " + ap0 + ");");
-                e.line(pad + "    " + lg(k) + " = fma(" + p0 + ", " + bpar + ", " + lg(k) + ");");
-            }
+            e.line(pad + "    " + lg(k) + " = fma(" + p0 + ", " + bs + ", " + lg(k) + ");");
+            if (!bpar.empty()) e.line(pad + "    " + g + " = fma(" + p0 + ", " + xr(k) + ", " + g + ");");
             e.line(pad + "  }");
         }
+        if (gather) e.line(pad + "  " + ap0 + " = fma(" + g + ", " + rc + ", " + ap0 + ");");
         e.line(pad + "}");
     }
     std::string backward_step(int index) const
