@@ -123,6 +123,15 @@ int64_t psig_kernel_launches(void);
  * Both synchronise the device; neither belongs in a hot loop. */
 int64_t psig_bulk_copy_timeouts(void);
 int psig_set_bulk_wait_polls(int polls);
+/* Diagnostic, host only, no counterpart in the reference.  For a description whose top degree is a word
+ * list over dense lower degrees (the LogSignature row layout) served by the register-tiled kernels, the
+ * threads of a unit that own no listed word skip the arithmetic of the top target degree; the launcher
+ * orders the unit's work items so that the skipping threads fill whole warps.  This call returns that
+ * order for the forward (backward == 0) or the reverse sweep: items[s] = work item of thread slot s
+ * (256 entries), *active = slots that run the top degree (a multiple of 32; at least the block size when
+ * nothing is skipped, e.g. without desc->words_host).  Returns the block size, or PSIG_ERR_UNSUPPORTED
+ * when the tiled kernels do not serve the description with a projected top degree. */
+int psig_tiled_top_plan(const PsigSigDesc *desc, int backward, unsigned char *items, int *active);
 const char *psig_status_string(int status);
 
 /* Width D of one signature row for this description, or a negative PsigStatus. */

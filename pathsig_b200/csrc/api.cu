@@ -145,6 +145,15 @@ int64_t psig_bulk_copy_timeouts(void) { return tiled_bulk_copy_timeouts(); }
 
 int psig_set_bulk_wait_polls(int polls) { return tiled_set_bulk_wait_polls(polls); }
 
+int psig_tiled_top_plan(const PsigSigDesc *desc, int backward, unsigned char *items, int *active)
+{
+    if (!desc || !items || !active) return PSIG_ERR_NULL;
+    LevelTable lt;
+    const int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    return tiled_top_plan(*desc, backward != 0, items, active);
+}
+
 const char *psig_status_string(int status)
 {
     switch (status) {

@@ -67,6 +67,7 @@ int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
 // Bounded wait of the bulk-copy staging: poll limit (test hook) and read-and-clear count of waits that ran out.
 int tiled_set_bulk_wait_polls(int polls);
 long long tiled_bulk_copy_timeouts();
+int tiled_top_plan(const PsigSigDesc &desc, bool backward, unsigned char *items, int *active);
 template <typename T>
 int tiled_sig_backward(const PsigSigDesc &desc, const T *path, const T *sig, const T *grad, T *grad_path,
                        void *workspace, cudaStream_t stream);

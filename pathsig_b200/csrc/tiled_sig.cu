@@ -64,6 +64,12 @@ bool tiled_supported(const PsigSigDesc &desc)
 
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &) { return 0; }
 
+int tiled_top_plan(const PsigSigDesc &desc, bool backward, unsigned char *items, int *active)
+{
+    return desc.dtype == PSIG_F32 ? f32::top_plan_of(desc, backward, items, active)
+                                  : f64::top_plan_of(desc, backward, items, active);
+}
+
 int tiled_set_bulk_wait_polls(int polls)
 {
     const int rc = f32::bulk_wait_control(true, polls, nullptr);

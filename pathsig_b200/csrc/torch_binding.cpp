@@ -15,6 +15,7 @@
 #include <c10/cuda/CUDAGraphsC10Utils.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <atomic>
 #include <list>
@@ -27,6 +28,15 @@
 namespace {
 
 std::atomic<int> g_algo{PSIG_ALGO_AUTO};
+
+// NVTX range around an operator call (host side: validation, allocation, enqueue), so that a timeline
+// shows which operator a kernel belongs to.  Costs nothing measurable without a tool attached.
+struct Range {
+    explicit Range(const char *name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
+    Range(const Range &) = delete;
+    Range &operator=(const Range &) = delete;
+};
 
 void check(int64_t status, const char *what)
 {
@@ -154,6 +164,7 @@ PsigSigDesc sig_desc(const at::Tensor &path, int64_t depth, bool alt, const at::
 at::Tensor compute_signature(const at::Tensor &path_in, int64_t depth, bool alt, const at::Tensor &encoded_words,
                              at::IntArrayRef level_sizes, bool use_windows, const at::Tensor &windows)
 {
+    Range range("pathsig_b200::compute_signature");
     TORCH_CHECK(path_in.is_cuda(), "path must be CUDA");
     c10::cuda::CUDAGuard guard(path_in.device());
     at::Tensor path = path_in.contiguous();
@@ -170,6 +181,7 @@ at::Tensor signature_backward(const at::Tensor &path_in, const at::Tensor &signa
                               int64_t depth, bool alt, const at::Tensor &encoded_words, at::IntArrayRef level_sizes,
                               bool use_windows, const at::Tensor &windows)
 {
+    Range range("pathsig_b200::signature_backward");
     TORCH_CHECK(path_in.is_cuda(), "path must be CUDA");
     TORCH_CHECK(signature_in.is_cuda(), "signature must be CUDA");
     TORCH_CHECK(grad_in.is_cuda(), "grad_signature must be CUDA");
@@ -236,6 +248,7 @@ std::vector<int64_t> with_last(const at::Tensor &t, int64_t last)
 std::tuple<at::Tensor, at::Tensor> sig_to_logsig(const at::Tensor &signature_in, int64_t depth, int64_t d, bool alt,
                                                  const at::Tensor &encoded_words, at::IntArrayRef level_sizes)
 {
+    Range range("pathsig_b200::sig_to_logsig");
     TORCH_CHECK(signature_in.is_cuda(), "signature must be CUDA");
     c10::cuda::CUDAGuard guard(signature_in.device());
     at::Tensor sig = signature_in.contiguous();
@@ -255,6 +268,7 @@ std::tuple<at::Tensor, at::Tensor> sig_to_logsig(const at::Tensor &signature_in,
 at::Tensor logsig_backward(const at::Tensor &signature_in, const at::Tensor &P_in, const at::Tensor &grad_in, int64_t depth,
                            bool alt, const at::Tensor &encoded_words, at::IntArrayRef level_sizes)
 {
+    Range range("pathsig_b200::logsig_backward");
     TORCH_CHECK(signature_in.is_cuda(), "sig must be CUDA");
     TORCH_CHECK(P_in.is_cuda(), "P must be CUDA");
     TORCH_CHECK(grad_in.is_cuda(), "grad_logsig must be CUDA");
@@ -304,6 +318,7 @@ PsigLogDesc projected_log_desc(const at::Tensor &sig, int64_t depth, int64_t d, 
 at::Tensor logsig_projected(const at::Tensor &signature_in, int64_t depth, int64_t d, const at::Tensor &top_words,
                             at::IntArrayRef level_sizes, const at::Tensor &lower_columns)
 {
+    Range range("pathsig_b200::logsig_projected");
     TORCH_CHECK(signature_in.is_cuda(), "signature must be CUDA");
     c10::cuda::CUDAGuard guard(signature_in.device());
     at::Tensor sig = signature_in.contiguous();
@@ -322,6 +337,7 @@ at::Tensor logsig_projected(const at::Tensor &signature_in, int64_t depth, int64
 at::Tensor logsig_projected_backward(const at::Tensor &signature_in, const at::Tensor &grad_in, int64_t depth, int64_t d,
                                      const at::Tensor &top_words, at::IntArrayRef level_sizes, const at::Tensor &lower_columns)
 {
+    Range range("pathsig_b200::logsig_projected_backward");
     TORCH_CHECK(signature_in.is_cuda() && grad_in.is_cuda(), "signature and grad_out must be CUDA");
     TORCH_CHECK(grad_in.scalar_type() == signature_in.scalar_type(), "grad_out must have same dtype as signature");
     same_device(signature_in, grad_in, "grad_out");
@@ -358,6 +374,7 @@ PsigChenDesc chen_desc(const at::Tensor &a, const at::Tensor &b, int64_t depth, 
 
 at::Tensor chen_product(const at::Tensor &sig_a, const at::Tensor &sig_b, int64_t depth, int64_t d)
 {
+    Range range("pathsig_b200::chen_product");
     PsigChenDesc desc = chen_desc(sig_a, sig_b, depth, d);
     c10::cuda::CUDAGuard guard(sig_a.device());
     at::Tensor a = sig_a.contiguous(), b = sig_b.contiguous(), out = at::empty_like(a);
@@ -369,6 +386,7 @@ at::Tensor chen_product(const at::Tensor &sig_a, const at::Tensor &sig_b, int64_
 std::tuple<at::Tensor, at::Tensor> chen_product_backward(const at::Tensor &sig_a, const at::Tensor &sig_b,
                                                          const at::Tensor &grad_out, int64_t depth, int64_t d)
 {
+    Range range("pathsig_b200::chen_product_backward");
     PsigChenDesc desc = chen_desc(sig_a, sig_b, depth, d);
     TORCH_CHECK(grad_out.is_cuda(), "grad_out must be CUDA");
     TORCH_CHECK(grad_out.scalar_type() == sig_a.scalar_type() && grad_out.sizes() == sig_a.sizes(),

@@ -297,3 +297,41 @@ def test_compiled_closure_kernels_are_kept_on_disk(tmp_path, monkeypatch):
     assert len(list((tmp_path / "kernels").glob("closure_*.cubin"))) == 2     # forward and backward pass
     assert lib.psig_closure_compile(buf.value, b"sm_100a", log, 1 << 14) == 0
     assert log.value.count(b"read from") == 2
+
+
+def test_top_plan_orders_owners_of_listed_words_first():
+    """Projected top degree on the tiled kernels: the launcher's order of a unit's work items puts the
+    threads that own a listed word first and lets whole warps of the others skip the top degree.  For the
+    Lyndon words of length 6 over 4 letters, 29 of the 64 prefixes of length 3 start a Lyndon word (a
+    Lyndon word's first letter is its smallest), so one of the two warps skips."""
+    import ctypes
+
+    from pathsig_b200 import _load
+    lib = _load.ensure_loaded()
+    proj = ps.projections.lyndon(6, 4, device="cpu")
+    sizes = list(proj.level_sizes)
+    top = proj.encoded_words[-sizes[6]:].tolist()
+    ext = [0] + [4 ** k for k in range(1, 6)] + [len(top)]
+    desc, keep = _closure_desc(top, ext, 4, 6)
+    items = (ctypes.c_ubyte * 256)()
+    active = ctypes.c_int(0)
+    for backward in (0, 1):
+        nt = lib.psig_tiled_top_plan(ctypes.byref(desc), backward, items, ctypes.byref(active))
+        assert nt == 64 and active.value == 32
+        order = list(items)[:64]
+        assert sorted(order) == list(range(64))                        # a permutation of the unit's items
+        owners = sorted({code // 64 for code in top})                   # prefixes of length 3 with a listed word
+        assert len(owners) == 29 and order[:29] == owners               # owners first, in their own order
+        assert all(min(u // 16, (u // 4) % 4, u % 4) == u // 16 for u in owners)
+    # without a host copy of the list nothing is reordered and nothing is skipped
+    desc.words_host = None
+    assert lib.psig_tiled_top_plan(ctypes.byref(desc), 0, items, ctypes.byref(active)) == 64
+    assert active.value >= 64 and list(items)[:64] == list(range(64))
+    # every prefix owns a word: nothing to skip either
+    dense_top = list(range(0, 4 ** 6, 7))
+    desc, keep = _closure_desc(dense_top, [0] + [4 ** k for k in range(1, 6)] + [len(dense_top)], 4, 6)
+    assert lib.psig_tiled_top_plan(ctypes.byref(desc), 1, items, ctypes.byref(active)) == 64
+    assert active.value >= 64
+    # a shape whose unit spans several blocks has no projected-top path on the tiled kernels
+    desc, keep = _closure_desc([1, 2, 3], [0, 16, 256, 4096, 3], 16, 4)
+    assert lib.psig_tiled_top_plan(ctypes.byref(desc), 0, items, ctypes.byref(active)) < 0
