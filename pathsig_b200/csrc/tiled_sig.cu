@@ -30,6 +30,7 @@
 #include "common.cuh"
 
 #include <cstdint>
+#include <type_traits>
 
 namespace psig {
 namespace {

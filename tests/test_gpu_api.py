@@ -368,3 +368,38 @@ def test_bounded_wait_of_the_bulk_staging_runs_out_harmlessly(ps, oracle):
     widths = util.level_widths(8, 4)
     assert max(util.level_rel_errors(out_short, want, widths)) < 1e-5
     assert torch.equal(out_short, out_default)                          # same bytes, same arithmetic
+
+
+@pytest.mark.parametrize("algo", ["tiled", "generic", "closure"])
+def test_run_to_run_reproducibility(ps, algo):
+    """What is promised about bits: the forward pass of every kernel family gives the same bytes on every run,
+    and so does the tiled backward when one block holds the unit and no windows overlap (its sums run in a fixed
+    order and it stores instead of adding).  The paths that add with float atomics (overlapping windows, the
+    generic and closure backward) are only checked to agree within the float32 tolerance."""
+    d, depth = (3, 4) if algo == "closure" else (8, 4)   # a small word tree keeps the run-time compilation short
+    x = util.brownian_path(64, 200, d, seed=5, dtype=torch.float32).to(DEV)
+    win = util.sliding_windows(200, 64, 16, device=DEV)
+    ps.ops.set_algorithm(algo)
+    try:
+        for windows in (None, win):
+            mod = ps.Signature(depth=depth, windows=windows)
+            outs, grads = [], []
+            for _ in range(3):
+                xr = x.clone().requires_grad_(True)
+                out = mod(xr)
+                g = util.normal_like(out.shape, 3, torch.float32).to(DEV)
+                (out * g).sum().backward()
+                outs.append(out.detach().clone())
+                grads.append(xr.grad.clone())
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+            if algo == "tiled" and windows is None:
+                assert torch.equal(grads[0], grads[1]) and torch.equal(grads[0], grads[2])
+            else:
+                assert util.rel_error(grads[1], grads[0]) < util.TOL[torch.float32]
+                assert util.rel_error(grads[2], grads[0]) < util.TOL[torch.float32]
+        # the logarithm (row in shared memory) is reproducible forward
+        log = ps.LogSignature(depth=depth)
+        a, b = log(x), log(x)
+        assert torch.equal(a, b)
+    finally:
+        ps.ops.set_algorithm("auto")
