@@ -211,11 +211,13 @@ class Workload:
             return self.mod(self.x)
 
     def step_fwd_bwd(self, events=None):
-        """Forward + backward with dL/dout = G (the loss is sum(out * G)).  For the signature
-        modules the two operators are called directly; returns (output, grad wrt the path)."""
+        """Forward + backward with dL/dout = G (the loss is sum(out * G)).  For the dense signature
+        modules the two operators are called directly; projected and log-signature modules go through
+        the module and autograd (their forward is more than one operator).  Returns (output, grad wrt
+        the path)."""
         import pathsig_b200 as ps
         m = self.mod
-        if isinstance(m, ps.Signature):
+        if isinstance(m, ps.Signature) and not m.alternative_projection:
             sig = ps.ops.compute_signature(self.x, m.depth, m.alternative_projection, m._encoded_words,
                                            m._level_sizes, m.use_windows, m._windows)
             if events is not None:

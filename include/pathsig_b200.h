@@ -188,6 +188,8 @@ int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *c
  * device; the compiler's log goes to `log`.  Neither call launches anything. */
 int64_t psig_closure_source(const PsigSigDesc *desc, int target_bins, char *buffer, int64_t capacity, int64_t *stats);
 int psig_closure_compile(const char *source, const char *arch, char *log, int64_t log_capacity);
+/* 1 when the run-time compiler (libnvrtc.so.12) the prefix-closure kernels need can be loaded, else 0.  Host only. */
+int psig_closure_available(void);
 
 /* No counterpart in the reference.  Same result as psig_sig_backward computed by the generic
  * kernel, for callers that have no scratch memory to pass and may not allocate any: hosts whose

@@ -94,6 +94,7 @@ EXPORTS = {
     "psig_tiled_top_plan": (_int, [_SigP, _int, ctypes.POINTER(ctypes.c_ubyte), ctypes.POINTER(_int)]),
     "psig_closure_source": (_i64, [_SigP, _int, ctypes.c_char_p, _i64, ctypes.POINTER(ctypes.c_int64)]),
     "psig_closure_compile": (_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, _i64]),
+    "psig_closure_available": (_int, []),
     "psig_sig_backward_static": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp]),
     "psig_sig_backward_static_limit": (_i64, []),
     "psig_chen_size": (_i64, [_ChenP]),

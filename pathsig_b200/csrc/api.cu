@@ -190,6 +190,8 @@ int64_t psig_closure_source(const PsigSigDesc *desc, int target_bins, char *buff
     return n;
 }
 
+int psig_closure_available(void) { return closure_compiler_available() ? 1 : 0; }
+
 int psig_closure_compile(const char *source, const char *arch, char *log, int64_t log_capacity)
 {
     if (!source || !arch) return PSIG_ERR_NULL;

@@ -1170,6 +1170,9 @@ bool closure_supported(const PsigSigDesc &desc, const LevelTable &lt)
     return plan && plan->usable;
 }
 
+// Whether the run-time compiler the family depends on can be loaded (host only).
+bool closure_compiler_available() { return nvrtc().ok; }
+
 // Cheap test (no compilation) used by the automatic selection: dense rows, or projected rows with a host
 // copy of the codes; a closure of moderate size; enough work to repay the one-off compilation; and
 // channels few enough that a chunk of staged points fits shared memory.

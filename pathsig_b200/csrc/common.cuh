@@ -84,6 +84,7 @@ int closure_sig_backward(const PsigSigDesc &desc, const LevelTable &lt, const T 
 long long closure_source(const PsigSigDesc &desc, const LevelTable &lt, int target_bins, char *buffer, long long capacity,
                          long long *stats);
 int closure_compile_only(const char *text, const char *arch, char *log, long long log_capacity);
+bool closure_compiler_available();
 
 // Launch attributes of a kernel (opt-in dynamic shared memory above 48 KB, preference for the largest
 // shared-memory carveout) are properties of the function on a device: they are set the first time a

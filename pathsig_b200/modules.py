@@ -81,8 +81,66 @@ def _check_codes(codes: List[int], level_sizes: List[int], d: int, depth: int) -
         used += size
 
 
+_MAX_CLOSURE_WIDTH = 16384   # largest row the prefix-closure kernels are generated for
+_CLOSURE_MIN_UNITS = 256     # ... and the work below which the library does not select them
+_CLOSURE_MIN_WORK = 2.0e7
+
+
+def _prefix_closure(codes: List[int], level_sizes: List[int], d: int, depth: int):
+    """The requested words together with all their prefixes, in the row layout of the operators.
+
+    Returns ``(closure_codes, closure_level_sizes, columns)``: the codes of the incomplete degrees of the
+    closed set (ascending within a degree), its level sizes, and for every column of the requested row its
+    column in the closed row; or ``None`` when the set is already closed, lists a word twice, or would be
+    wider than the kernels generated for word sets accept."""
+    requested: List[Optional[List[int]]] = [None] * (depth + 1)   # None: complete degree
+    used = 0
+    for k in range(1, depth + 1):
+        size = int(level_sizes[k])
+        if size != d ** k:
+            requested[k] = codes[used: used + size]
+            used += size
+            if len(set(requested[k])) != size:
+                return None
+    closed: List[Optional[set]] = [None if requested[k] is None else set(requested[k]) for k in range(depth + 1)]
+    closed[0] = set()
+    for k in range(depth, 1, -1):
+        if closed[k - 1] is None:
+            continue
+        if closed[k] is None:
+            closed[k - 1] = None      # every word of degree k is wanted: so is every word below it
+            continue
+        closed[k - 1].update(c // d for c in closed[k])
+        if len(closed[k - 1]) == d ** (k - 1):
+            closed[k - 1] = None
+    sizes = [0] + [d ** k if closed[k] is None else len(closed[k]) for k in range(1, depth + 1)]
+    if sizes == [0] + [int(v) for v in level_sizes[1: depth + 1]] or sum(sizes) > _MAX_CLOSURE_WIDTH:
+        return None
+    closure_codes: List[int] = []
+    columns: List[int] = []
+    offset = 0
+    for k in range(1, depth + 1):
+        if closed[k] is None:
+            position = None
+        else:
+            ordered = sorted(closed[k])
+            closure_codes.extend(ordered)
+            position = {c: i for i, c in enumerate(ordered)}
+        wanted = range(d ** k) if requested[k] is None else requested[k]
+        columns.extend(offset + (c if position is None else position[c]) for c in wanted)
+        offset += sizes[k]
+    return closure_codes, sizes, columns
+
+
 class Signature(nn.Module):
-    """Truncated signature of a batch of paths ``(B, L, d)`` -> ``(B, D)`` or ``(B, W, D)``."""
+    """Truncated signature of a batch of paths ``(B, L, d)`` -> ``(B, D)`` or ``(B, W, D)``.
+
+    With a projection whose words have prefixes that are not requested themselves, large enough problems
+    are evaluated on the prefix closure of the word set and the requested columns are selected from that
+    row: the kernels generated for a word set compute every prefix anyway, and with all of them in the
+    saved signature the backward pass does not have to rebuild them with a second forward sweep (the
+    reference recomputes them inside its backward kernel, ``recompute_sig`` in
+    ``src/pathsig/backward/sig_backward_kernels.cu:204-318``)."""
 
     def __init__(self, *, depth: int, projection=None, windows=None):
         super().__init__()
@@ -94,18 +152,49 @@ class Signature(nn.Module):
         self.register_buffer("_encoded_words", words if self.alternative_projection else _no_words(),
                              persistent=self.alternative_projection)
         self._level_sizes: List[int] = projection.level_sizes if self.alternative_projection else []
+        self._closure_sizes: Optional[List[int]] = None
         if self.alternative_projection:
-            _check_codes(_host_codes(projection, words), self._level_sizes, int(projection.path_dim), self.depth)
+            codes = _host_codes(projection, words)
+            _check_codes(codes, self._level_sizes, int(projection.path_dim), self.depth)
+            self._refresh_closure(codes)
             self.register_load_state_dict_post_hook(_recheck_loaded_words)
 
+    def _refresh_closure(self, codes: List[int]) -> None:
+        """Derived from the word codes actually in the buffer (re-derived after load_state_dict)."""
+        d = int(self.projection.path_dim)
+        device = self._encoded_words.device
+        plan = _prefix_closure(codes, self._level_sizes, d, self.depth) if d <= 64 else None
+        if plan is not None and not ops_module.closure_kernels_available():
+            plan = None
+        self._closure_sizes = None if plan is None else plan[1]
+        self.register_buffer("_closure_words", torch.tensor([] if plan is None else plan[0], dtype=torch.int64,
+                                                            device=device), persistent=False)
+        self.register_buffer("_closure_columns", torch.tensor([] if plan is None else plan[2], dtype=torch.int64,
+                                                              device=device), persistent=False)
+
+    def _closure_pays(self, path: torch.Tensor) -> bool:
+        """The library's own rule for selecting the kernels generated for a word set, on the closed row."""
+        if self._closure_sizes is None or path.dim() != 3 or ops_module._algo not in ops_module.CLOSURE_ALGOS:
+            return False
+        units = path.shape[0] * (self._windows.shape[0] if self.use_windows else 1)
+        work = float(units) * float(path.shape[1] - 1) * float(sum(self._closure_sizes))
+        return units >= _CLOSURE_MIN_UNITS and work >= _CLOSURE_MIN_WORK
+
     def forward(self, path: torch.Tensor) -> torch.Tensor:
+        if self._closure_pays(path):
+            closed = compute_signature(path, self.depth, True, self._closure_words, self._closure_sizes,
+                                       self.use_windows, self._windows)
+            return _SelectColumns.apply(closed, self._closure_columns)
         return compute_signature(path, self.depth, self.alternative_projection, self._encoded_words,
                                  self._level_sizes, self.use_windows, self._windows)
 
 
 def _recheck_loaded_words(module, incompatible_keys) -> None:
     """After load_state_dict: the word codes now in the buffers must still be words of this projection."""
-    _check_codes(module._encoded_words.tolist(), module._level_sizes, int(module.projection.path_dim), module.depth)
+    codes = module._encoded_words.tolist()
+    _check_codes(codes, module._level_sizes, int(module.projection.path_dim), module.depth)
+    if isinstance(module, Signature):
+        module._refresh_closure(codes)
     if isinstance(module, LogSignature):
         top = module._top_words.tolist()
         full = int(module.projection.path_dim) ** module.depth

@@ -57,6 +57,12 @@ _SCHEMAS = {
 # Tests flip it to compare the register-tiled kernels with the generic ones.  The compiled operator layer
 # holds the value it acts on; this copy serves the shape queries made from Python.
 _algo = _load.ALGO_AUTO
+CLOSURE_ALGOS = (_load.ALGO_AUTO, _load.ALGO_CLOSURE)   # selections under which a word set can get generated kernels
+
+
+def closure_kernels_available() -> bool:
+    """Whether the run-time compiler the prefix-closure kernels need can be loaded on this machine."""
+    return bool(_load.ensure_loaded().psig_closure_available())
 
 
 def set_algorithm(name: str) -> None:

@@ -162,3 +162,53 @@ def test_dense_shape_without_a_tiled_instance_takes_the_closure_kernels(ps, d, d
     assert torch.equal(out_a, out_c)
     assert max(util.level_rel_errors(out_c, out_g, util.level_widths(d, depth))) < 1e-5
     assert util.rel_error(grad_c, grad_g) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("windowed", [False, True])
+def test_module_evaluates_large_projections_on_the_closed_word_set(ps, oracle, dtype, windowed):
+    """``Signature`` with a projection whose words have prefixes that are not requested: a problem large
+    enough for the generated kernels runs on the prefix closure of the word set (so that the backward
+    pass finds every prefix in the saved signature) and selects the requested columns; values and
+    input gradient match the oracle on the requested layout, and the plain operator call."""
+    words = util.random_words(90, 5, 2, 5, seed=21)
+    proj = ps.projections.words(words, 5, 5, full_levels=(1,), device=DEV)
+    B, L = (128, 200) if windowed else (512, 300)
+    win = util.sliding_windows(L, 60, 10, device=DEV) if windowed else None
+    x = util.brownian_path(B, L, 5, seed=2, dtype=dtype).to(DEV)
+    mod = ps.Signature(depth=5, projection=proj, windows=win)
+    assert mod._closure_sizes is not None and sum(mod._closure_sizes) > sum(proj.level_sizes[1:])
+    assert mod._closure_pays(x) and not mod._closure_pays(x[:4])
+    xa = x.clone().requires_grad_(True)
+    out = mod(xa)
+    g = util.normal_like(out.shape, 4, dtype).to(DEV)
+    out.backward(g)
+    # the operator on the requested word set itself
+    xb = x.clone().requires_grad_(True)
+    plain = ps.ops.compute_signature(xb, 5, True, mod._encoded_words, mod._level_sizes, mod.use_windows, mod._windows)
+    plain.backward(g)
+    tol = util.TOL[dtype]
+    assert out.shape == plain.shape
+    assert util.rel_error(out, plain) < tol and util.rel_error(xa.grad, xb.grad) < tol
+    rows = slice(0, 6)
+    xs = x[rows].double().cpu()
+    win_cpu = None if win is None else win.cpu()
+    want = oracle.sig_forward(xs, 5, proj.encoded_words.cpu(), list(proj.level_sizes), win_cpu)
+    assert util.rel_error(out[rows], want) < tol
+    want_grad = oracle.sig_backward(xs, want, g[rows].double().cpu(), 5, proj.encoded_words.cpu(),
+                                    list(proj.level_sizes), win_cpu)
+    assert util.rel_error(xa.grad[rows], want_grad) < tol
+    # a small problem takes the requested word set as it is
+    small = mod(x[:4])
+    assert util.rel_error(small, out[:4]) < tol
+    # the closed set is re-derived from the codes a state_dict brings: a module built for another word set
+    # with the same level sizes (one word replaced by an unused word of its length) takes over this one's
+    longest = max(words, key=len)
+    swapped = next(w for w in (longest[:-1] + (a,) for a in range(5)) if w not in set(words))
+    other_proj = ps.projections.words([swapped if w == longest else w for w in words], 5, 5, full_levels=(1,), device=DEV)
+    assert list(other_proj.level_sizes) == list(proj.level_sizes)
+    other = ps.Signature(depth=5, projection=other_proj, windows=win)
+    assert not torch.equal(other._encoded_words, mod._encoded_words)
+    other.load_state_dict(mod.state_dict())
+    assert torch.equal(other._closure_words, mod._closure_words) and torch.equal(other._closure_columns, mod._closure_columns)
+    assert util.rel_error(other(x), out) < tol

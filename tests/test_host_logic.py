@@ -335,3 +335,26 @@ def test_top_plan_orders_owners_of_listed_words_first():
     # a shape whose unit spans several blocks has no projected-top path on the tiled kernels
     desc, keep = _closure_desc([1, 2, 3], [0, 16, 256, 4096, 3], 16, 4)
     assert lib.psig_tiled_top_plan(ctypes.byref(desc), 0, items, ctypes.byref(active)) < 0
+
+
+def test_prefix_closure_of_a_word_set():
+    """The closed word set ``Signature`` evaluates large projections on: every prefix of a requested word,
+    complete degrees below a complete degree, columns of the requested row inside the closed row."""
+    from pathsig_b200.modules import _prefix_closure
+    # d = 3: degree 1 complete, (0,1) at degree 2, (1,0,0) and (1,0,2) at degree 3
+    closed = _prefix_closure([1, 9, 11], [0, 3, 1, 2], 3, 3)
+    assert closed == ([1, 3, 9, 11], [0, 3, 2, 2], [0, 1, 2, 3, 5, 6])
+    assert _prefix_closure([1, 3, 9, 11], [0, 3, 2, 2], 3, 3) is None          # already closed
+    assert _prefix_closure([9, 9], [0, 3, 9, 2], 3, 3) is None                  # a word listed twice
+    # a complete degree above an incomplete one makes everything below complete
+    codes, sizes, cols = _prefix_closure([1], [0, 1, 9], 3, 2)
+    assert sizes == [0, 3, 9] and codes == [] and cols == [1] + list(range(3, 12))
+    # no degree-1 word requested at all: its prefixes appear, the requested columns move behind them
+    codes, sizes, cols = _prefix_closure([5, 7], [0, 0, 2], 3, 2)
+    assert sizes == [0, 2, 2] and codes == [1, 2, 5, 7] and cols == [2, 3]
+    # the benchmark's word list: 482 words in the closed set, as the kernel generator counts
+    import bench
+    wl = bench.Workload("cfg3")
+    proj = ps.projections.words([w for w in wl.words if len(w) > 1], 6, 8, full_levels=(1,), device="cpu")
+    codes, sizes, cols = _prefix_closure(proj.encoded_words.tolist(), list(proj.level_sizes), 8, 6)
+    assert sum(sizes) == 482 and len(cols) == 208 and len(set(cols)) == 208 and cols == sorted(cols)
