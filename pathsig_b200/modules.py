@@ -84,6 +84,7 @@ def _check_codes(codes: List[int], level_sizes: List[int], d: int, depth: int) -
 _MAX_CLOSURE_WIDTH = 16384   # largest row the prefix-closure kernels are generated for
 _CLOSURE_MIN_UNITS = 256     # ... and the work below which the library does not select them
 _CLOSURE_MIN_WORK = 2.0e7
+_MAX_CLOSURE_GROWTH = 4       # the closed row may be at most this many times as wide as the requested one
 
 
 def _prefix_closure(codes: List[int], level_sizes: List[int], d: int, depth: int):
@@ -91,8 +92,8 @@ def _prefix_closure(codes: List[int], level_sizes: List[int], d: int, depth: int
 
     Returns ``(closure_codes, closure_level_sizes, columns)``: the codes of the incomplete degrees of the
     closed set (ascending within a degree), its level sizes, and for every column of the requested row its
-    column in the closed row; or ``None`` when the set is already closed, lists a word twice, or would be
-    wider than the kernels generated for word sets accept."""
+    column in the closed row; or ``None`` when the set is already closed, lists a word twice, would be
+    wider than the kernels generated for word sets accept, or more than four times as wide as the request."""
     requested: List[Optional[List[int]]] = [None] * (depth + 1)   # None: complete degree
     used = 0
     for k in range(1, depth + 1):
@@ -114,8 +115,11 @@ def _prefix_closure(codes: List[int], level_sizes: List[int], d: int, depth: int
         if len(closed[k - 1]) == d ** (k - 1):
             closed[k - 1] = None
     sizes = [0] + [d ** k if closed[k] is None else len(closed[k]) for k in range(1, depth + 1)]
+    requested_width = sum(int(v) for v in level_sizes[1: depth + 1])
     if sizes == [0] + [int(v) for v in level_sizes[1: depth + 1]] or sum(sizes) > _MAX_CLOSURE_WIDTH:
         return None
+    if sum(sizes) > _MAX_CLOSURE_GROWTH * requested_width:
+        return None   # the saved signature would cost much more memory than the one that was asked for
     closure_codes: List[int] = []
     columns: List[int] = []
     offset = 0

@@ -212,3 +212,24 @@ def test_module_evaluates_large_projections_on_the_closed_word_set(ps, oracle, d
     other.load_state_dict(mod.state_dict())
     assert torch.equal(other._closure_words, mod._closure_words) and torch.equal(other._closure_columns, mod._closure_columns)
     assert util.rel_error(other(x), out) < tol
+
+
+def test_closed_word_set_path_traces_under_torch_compile(ps):
+    """The module's choice between the requested and the closed word set is shape arithmetic in Python and
+    its column selection a custom autograd function: both trace without graph breaks, and the compiled
+    function gives the eager values and gradient."""
+    proj = ps.projections.words(util.random_words(90, 5, 2, 5, seed=21), 5, 5, full_levels=(1,), device=DEV)
+    mod = ps.Signature(depth=5, projection=proj)
+    x1 = util.brownian_path(512, 300, 5, seed=2, dtype=torch.float32).to(DEV).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    assert mod._closure_pays(x1)
+
+    def fn(x):
+        return mod(x).square().sum()
+
+    compiled = torch.compile(fn, backend="aot_eager", fullgraph=True)
+    y1, y2 = fn(x1), compiled(x2)
+    y1.backward()
+    y2.backward()
+    assert torch.allclose(y1, y2, rtol=1e-5)
+    assert util.rel_error(x2.grad, x1.grad) < util.TOL[torch.float32]
