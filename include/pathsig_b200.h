@@ -157,9 +157,11 @@ int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
 int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
                       void *grad_path, void *workspace, int64_t workspace_bytes, void *stream);
 
-/* Scalars per row of the cache that psig_logsig_forward fills for psig_logsig_backward: S*depth (the
- * powers P_m of the reference) for the global-memory kernels, 0 for the row-in-shared-memory kernels,
- * which recompute what they need.  Host-only; depends on the description alone. */
+/* Scalars per row of the cache argument of psig_logsig_forward / psig_logsig_backward: 0 when the row
+ * fits the row-in-shared-memory form of the kernels; S*depth -- the shape of the reference's table of
+ * powers P_m, so that operator signatures stay the same -- when the row is streamed through global
+ * memory, where the forward pass uses part of it as scratch (the backward pass reads nothing from it
+ * and recomputes what it needs in its own workspace).  Host-only; depends on the description alone. */
 int64_t psig_logsig_cache_size(const PsigLogDesc *desc);
 
 /* logsig (rows, S) = word coordinates of the truncated tensor logarithm of `sig` (rows, S);

@@ -322,8 +322,10 @@ int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc)
     LevelTable lt;
     const int rc = log_table(desc, &lt);
     if (rc != PSIG_OK) return rc;
-    if (horner_logsig_supported(*desc, lt)) return 0;  // the row-in-shared-memory kernel needs none
-    return (int64_t)dtype_size(desc->dtype) * desc->rows * lt.total * desc->depth;
+    if (horner_logsig_supported(*desc, lt)) return 0;  // the row-in-shared-memory form needs none
+    const long long scalars = streamed_logsig_backward_scratch(*desc, lt);
+    if (scalars < 0) return PSIG_ERR_TOO_LARGE;
+    return (int64_t)dtype_size(desc->dtype) * scalars;
 }
 
 int psig_logsig_backward(const PsigLogDesc *desc, const void *sig, const void *cache, const void *grad_logsig,

@@ -49,14 +49,19 @@ template <typename T>
 int generic_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *cache,
                             const T *grad_logsig, T *grad_sig, T *grad_cache_ws, cudaStream_t stream);
 
-// Row-in-shared-memory log-signature kernels (horner_logsig.cu); `supported` is a pure function
-// of the description, so forward and backward of one call always agree on the kernel family.
+// Horner-form log-signature kernels (horner_logsig.cu).  `supported` tells whether the row fits shared
+// memory; it is a pure function of the description, so forward and backward of one call always agree
+// on the form.  With `scratch` null the row-in-shared-memory form runs; otherwise the streamed form, on
+// streamed_logsig_*_scratch() scalars of global memory (negative: the row does not fit 32-bit positions).
 bool horner_logsig_supported(const PsigLogDesc &desc, const LevelTable &lt);
+long long streamed_logsig_forward_scratch(const PsigLogDesc &desc, const LevelTable &lt);
+long long streamed_logsig_backward_scratch(const PsigLogDesc &desc, const LevelTable &lt);
 template <typename T>
-int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, cudaStream_t stream);
+int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, T *scratch,
+                          cudaStream_t stream);
 template <typename T>
 int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *grad_logsig,
-                           T *grad_sig, cudaStream_t stream);
+                           T *grad_sig, T *scratch, cudaStream_t stream);
 
 // Register-tiled dense kernels, float32 and float64 (tiled_sig.cu).  `supported` tells whether a kernel
 // exists for this description (dense, or dense below a projected top degree).

@@ -15,8 +15,9 @@
 // incoming gradient, no atomics) except for the words of a projected top degree, which scatter
 // with shared-memory atomics.  The T_k are recomputed, not stored.
 //
-// Used when the per-row shared memory fits and word codes fit 32 bits; otherwise the global-memory
-// kernels of generic_logsig.cu run.
+// Rows whose lower degrees do not fit shared memory run the same kernels in "streamed" form: the buffers
+// are per-row scratch in global memory (the caller's cache / workspace) and x is read from the signature
+// row itself.  Word codes and row positions must fit 32 bits (rows below 2^31 scalars).
 #include "common.cuh"
 
 namespace psig {
@@ -263,18 +264,23 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
 
 template <typename T, int NMAX>
 __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
-                                                                      T *__restrict__ logsig)
+                                                                      T *__restrict__ logsig, T *scratch)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T *xs = reinterpret_cast<T *>(smem_raw);
-    T *ta = xs + p.lower;
-    T *tb = ta + p.lower;
+    // `scratch` null: the row's lower degrees and the two T buffers live in shared memory.  Otherwise
+    // (rows too large for that) x is read from the signature row itself and the T buffers are this
+    // row's 2*lower scalars of `scratch` in global memory -- the same code on other pointers.
+    T *const xs_copy = reinterpret_cast<T *>(smem_raw);
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
         T *l = logsig + row * p.out_width;
+        const T *xs = scratch ? s : xs_copy;
+        T *ta = scratch ? scratch + row * 2 * (long long)p.lower : xs_copy + p.lower;
+        T *tb = ta + p.lower;
         __syncthreads();  // the previous row's readers are done with the buffers
-        for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) xs[i] = s[i];
+        if (!scratch)
+            for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) xs_copy[i] = s[i];
         __syncthreads();
         const T *t1 = build_t<T, NMAX>(p, xs, ta, tb, nullptr);
         // log S = x (x) T_1: degrees below N from shared memory, the top degree streamed
@@ -406,26 +412,30 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
 template <typename T, int NMAX>
 __global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
-                                                                       T *__restrict__ gsig)
+                                                                       T *__restrict__ gsig, T *scratch)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T *xs = reinterpret_cast<T *>(smem_raw);  // x, degrees below N
-    T *gl = xs + p.lower;                      // incoming gradient, degrees below N
-    T *gx = gl + p.lower;                      // gradient wrt x, degrees below N
-    T *ga = gx + p.lower;                      // adjoint of T_k
-    T *gb = ga + p.lower;                      // adjoint of T_{k+1}
-    T *tk = gb + p.lower;                      // every T_k (degrees 1..N-k) at t_off[k]
-    T *gts = tk + p.t_total;                   // dense top degree of the incoming gradient (when staged)
+    // `scratch` null: every buffer below lives in shared memory.  Otherwise x is read from the signature
+    // row and the other buffers are this row's 4*lower + t_total scalars of `scratch` in global memory
+    // (the top degree of the incoming gradient is then never staged).
+    T *const xs_copy = reinterpret_cast<T *>(smem_raw);  // x, degrees below N
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
+        const T *xs = scratch ? s : xs_copy;
+        T *gl = scratch ? scratch + row * (4 * (long long)p.lower + p.t_total) : xs_copy + p.lower;  // incoming gradient, degrees below N
+        T *gx = gl + p.lower;                      // gradient wrt x, degrees below N
+        T *ga = gx + p.lower;                      // adjoint of T_k
+        T *gb = ga + p.lower;                      // adjoint of T_{k+1}
+        T *tk = gb + p.lower;                      // every T_k (degrees 1..N-k) at t_off[k]
+        T *gts = tk + p.t_total;                   // dense top degree of the incoming gradient (when staged)
         const T *g = glog + row * p.out_width;
         const T *gtop_global = g + p.out_lower;
         const T *gtop = p.stage_top ? gts : gtop_global;  // re-read N-1 times by each side of the adjoint
         T *out = gsig + row * p.width;
         __syncthreads();
         for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) {
-            xs[i] = s[i];
+            if (!scratch) xs_copy[i] = s[i];
             const T gi = p.low_cols != nullptr ? T(0) : g[i];
             gl[i] = gi;
             gx[i] = gi;   // log S = x * 1 + ...: the degree-0 term of T_1 is 1
@@ -624,17 +634,38 @@ bool horner_logsig_supported(const PsigLogDesc &desc, const LevelTable &lt)
     return scalar * (5 * (size_t)p.lower + p.t_total) <= kHornerMaxSmem;  // backward needs the most
 }
 
-template <typename T>
-int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, cudaStream_t stream)
+// Scalars of global scratch the streamed form needs per call, forward and backward, or a negative status
+// when word codes or row positions do not fit 32 bits (a row of 2^31 scalars or more).
+long long streamed_logsig_forward_scratch(const PsigLogDesc &desc, const LevelTable &lt)
 {
     HornerPlan p;
     const int rc = make_horner_plan(desc, lt, &p);
-    if (rc != PSIG_OK) return rc;
-    const size_t smem = forward_smem<T>(p);
+    if (rc != PSIG_OK) return PSIG_ERR_TOO_LARGE;
+    return desc.rows * 2 * (long long)p.lower;
+}
+
+long long streamed_logsig_backward_scratch(const PsigLogDesc &desc, const LevelTable &lt)
+{
+    HornerPlan p;
+    const int rc = make_horner_plan(desc, lt, &p);
+    if (rc != PSIG_OK) return PSIG_ERR_TOO_LARGE;
+    return desc.rows * (4 * (long long)p.lower + (long long)p.t_total);
+}
+
+// `scratch` null: the row-in-shared-memory form (the caller has checked horner_logsig_supported).
+// Otherwise the streamed form on streamed_logsig_forward_scratch() scalars of global memory.
+template <typename T>
+int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, T *logsig, T *scratch,
+                          cudaStream_t stream)
+{
+    HornerPlan p;
+    const int rc = make_horner_plan(desc, lt, &p);
+    if (rc != PSIG_OK) return scratch ? (int)PSIG_ERR_TOO_LARGE : rc;
+    const size_t smem = scratch ? 0 : forward_smem<T>(p);
     auto launch = [&](auto kernel) {
         // rows in flight are limited by shared memory under the default L1 split
-        if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, logsig);
+        if (smem > 0 && !prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, logsig, scratch);
         return check_launch();
     };
     if (p.depth <= 4) return launch(logsig_forward_horner<T, 4>);
@@ -645,19 +676,19 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
 
 template <typename T>
 int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const T *sig, const T *grad_logsig,
-                           T *grad_sig, cudaStream_t stream)
+                           T *grad_sig, T *scratch, cudaStream_t stream)
 {
     HornerPlan p;
     const int rc = make_horner_plan(desc, lt, &p);
-    if (rc != PSIG_OK) return rc;
+    if (rc != PSIG_OK) return scratch ? (int)PSIG_ERR_TOO_LARGE : rc;
     // the top degree is staged (dense, or as a dense image of the listed words) while the block stays
-    // under half of the largest supported footprint
-    p.stage_top = (p.depth >= 2 &&
+    // under half of the largest supported footprint; the streamed form reads it where it is
+    p.stage_top = (!scratch && p.depth >= 2 &&
                    sizeof(T) * (5 * (size_t)p.lower + p.t_total + (size_t)p.top_dense) <= kHornerMaxSmem / 2) ? 1u : 0u;
-    const size_t smem = backward_smem<T>(p);
+    const size_t smem = scratch ? 0 : backward_smem<T>(p);
     auto launch = [&](auto kernel) {
-        if (!prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, grad_logsig, grad_sig);
+        if (smem > 0 && !prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, grad_logsig, grad_sig, scratch);
         return check_launch();
     };
     if (p.depth <= 4) return launch(logsig_backward_horner<T, 4>);
@@ -667,12 +698,12 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
 }
 
 template int horner_logsig_backward<float>(const PsigLogDesc &, const LevelTable &, const float *, const float *,
-                                           float *, cudaStream_t);
+                                           float *, float *, cudaStream_t);
 template int horner_logsig_backward<double>(const PsigLogDesc &, const LevelTable &, const double *, const double *,
-                                            double *, cudaStream_t);
-template int horner_logsig_forward<float>(const PsigLogDesc &, const LevelTable &, const float *, float *,
+                                            double *, double *, cudaStream_t);
+template int horner_logsig_forward<float>(const PsigLogDesc &, const LevelTable &, const float *, float *, float *,
                                           cudaStream_t);
-template int horner_logsig_forward<double>(const PsigLogDesc &, const LevelTable &, const double *, double *,
+template int horner_logsig_forward<double>(const PsigLogDesc &, const LevelTable &, const double *, double *, double *,
                                            cudaStream_t);
 
 }  // namespace psig

@@ -283,8 +283,8 @@ at::Tensor logsig_backward(const at::Tensor &signature_in, const at::Tensor &P_i
     c10::cuda::CUDAGuard guard(signature_in.device());
     at::Tensor sig = signature_in.contiguous(), cache = P_in.contiguous(), grad = grad_in.contiguous();
     PsigLogDesc desc = log_desc(sig, depth, d, alt, encoded_words, level_sizes);
-    // The cache tells which kernel family produced it: the table of powers (S*depth per row) belongs to
-    // the global-memory kernels, an empty one to the row-in-shared-memory kernels.
+    // The cache tells which form of the kernels produced it: S*depth scalars per row belong to the form
+    // that streams through global scratch, an empty one to the row-in-shared-memory form.
     bool lead_ok = cache.dim() == sig.dim();
     for (int64_t i = 0; lead_ok && i + 1 < sig.dim(); ++i) lead_ok = cache.size(i) == sig.size(i);
     TORCH_CHECK(lead_ok && (cache.size(-1) == 0 || cache.size(-1) == sig.size(-1) * depth),

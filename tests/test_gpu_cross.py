@@ -1,6 +1,6 @@
 """Randomised cross-checks on the GPU between kernel families that compute the same thing by different
 routes: register-tiled against generic signature kernels (every tiled shape, both dtypes, ragged windows,
-lengths on both sides of the staging chunk), and the shared-memory against the table-of-powers
+lengths on both sides of the staging chunk), and the row-in-shared-memory against the streamed form of the
 log-signature kernels.  The oracle pins each family separately on a few shapes; this file widens the
 net cheaply, with seeded draws."""
 from __future__ import annotations

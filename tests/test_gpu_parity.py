@@ -115,7 +115,7 @@ def _oracle_logsig(oracle, mod, x64, g64, windows):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("d,depth,projected", [(2, 5, False), (3, 4, False), (3, 5, True), (4, 6, True), (5, 2, True)])
 @pytest.mark.parametrize("windowed", [False, True])
-@pytest.mark.parametrize("algo", ["auto", "generic"])  # row-in-shared-memory kernels / table-of-powers kernels
+@pytest.mark.parametrize("algo", ["auto", "generic"])  # row in shared memory / streamed through global scratch
 def test_logsignature(ps, oracle, dtype, d, depth, projected, windowed, algo):
     x = util.brownian_path(3, 21, d, seed=17 + d, dtype=dtype)
     win = util.sliding_windows(21, 9, 4) if windowed else None
@@ -130,6 +130,29 @@ def test_logsignature(ps, oracle, dtype, d, depth, projected, windowed, algo):
     finally:
         ps.ops.set_algorithm("auto")
     want, want_grad = _oracle_logsig(oracle, mod, x.double(), g.double(), win)
+    assert out.shape == want.shape
+    assert util.rel_error(out, want) < util.TOL[dtype]
+    assert util.rel_error(xg.grad, want_grad) < util.TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("projected", [False, True])
+def test_logsignature_of_rows_beyond_shared_memory(ps, oracle, dtype, projected):
+    """d = 6 at depth 6: the 9 330 scalars of the degrees below the top do not fit the shared-memory form
+    five times over, so the same Horner kernels run on global scratch (the operator's cache forward, its
+    workspace backward).  Values and input gradient against the oracle, dense and Lyndon top degree."""
+    from pathsig_b200 import _load
+    d, depth = 6, 6
+    x = util.brownian_path(2, 9, d, seed=29, dtype=dtype)
+    proj = ps.projections.lyndon(depth, d) if projected else None
+    mod = ps.LogSignature(depth=depth, projection=proj)
+    ls = mod._ext_level_sizes if projected else [0] + [d ** k for k in range(1, depth + 1)]
+    assert not ps.ops.logsig_projected_supported(dtype, depth, d, ls)      # the row does not fit shared memory
+    xg = x.to(DEV).requires_grad_(True)
+    out = mod(xg)
+    g = util.normal_like(out.shape, 31, dtype)
+    (out * g.to(DEV)).sum().backward()
+    want, want_grad = _oracle_logsig(oracle, mod, x.double(), g.double(), None)
     assert out.shape == want.shape
     assert util.rel_error(out, want) < util.TOL[dtype]
     assert util.rel_error(xg.grad, want_grad) < util.TOL[dtype]

@@ -50,12 +50,17 @@ def test_status_strings_and_sizes_without_a_gpu():
     ldesc.dtype, ldesc.d, ldesc.depth, ldesc.rows, ldesc.top_size = 1, 4, 6, 3, 670
     ldesc.top_words = 1 << 20
     assert lib.psig_logsig_size(ctypes.byref(ldesc)) == 1364 + 670
-    # rows small enough for the shared-memory kernels need no scratch; larger rows need the table of powers
+    # rows small enough for the shared-memory form need no scratch; larger rows are streamed through global
+    # scratch: four buffers of the degrees below the top plus every T_k (degrees 1..depth-k)
     assert lib.psig_logsig_backward_workspace(ctypes.byref(ldesc)) == 0
+    assert lib.psig_logsig_cache_size(ctypes.byref(ldesc)) == 0
     ldesc.d, ldesc.depth, ldesc.top_size, ldesc.top_words = 16, 5, 16 ** 5, None
     width = 16 + 16 ** 2 + 16 ** 3 + 16 ** 4 + 16 ** 5
+    lower = width - 16 ** 5
+    every_t = sum(sum(16 ** n for n in range(1, 5 - k + 1)) for k in range(1, 5))
     assert lib.psig_logsig_size(ctypes.byref(ldesc)) == width
-    assert lib.psig_logsig_backward_workspace(ctypes.byref(ldesc)) == 8 * 3 * width * 5
+    assert lib.psig_logsig_cache_size(ctypes.byref(ldesc)) == width * 5
+    assert lib.psig_logsig_backward_workspace(ctypes.byref(ldesc)) == 8 * 3 * (4 * lower + every_t)
 
 
 # ---- projections ----
