@@ -93,8 +93,9 @@ typedef struct PsigLogDesc {
     int32_t dtype;
     int32_t d;
     int32_t depth;
-    int32_t algo;               /* PsigAlgo: AUTO = row-in-shared-memory kernels when the row fits,
-                                   GENERIC = always the global-memory kernels (TILED is treated as AUTO) */
+    int32_t algo;               /* PsigAlgo: AUTO = row-in-shared-memory form of the kernels when the row fits,
+                                   GENERIC = always the form streamed through global scratch (TILED is
+                                   treated as AUTO) */
     int64_t rows;               /* B or B*W */
     int64_t top_size;           /* words kept at degree `depth` */
     const int64_t *top_words;   /* device codes of the top degree, or NULL when it is dense */
@@ -170,8 +171,9 @@ int64_t psig_logsig_cache_size(const PsigLogDesc *desc);
  * Replaces pathsig::sig_to_logsig (src/pathsig/forward/sig_launch.cu:230-339). */
 int psig_logsig_forward(const PsigLogDesc *desc, const void *sig, void *logsig, void *cache, void *stream);
 
-/* Scratch bytes psig_logsig_backward needs: rows * S * depth scalars for the global-memory
- * kernels, 0 for the row-in-shared-memory kernels. */
+/* Scratch bytes psig_logsig_backward needs: 0 for the row-in-shared-memory form; for the streamed form
+ * rows * (4 * lower + sum_k |T_k|) scalars, lower = the dense degrees below the top, T_k = degrees
+ * 1..depth-k.  PSIG_ERR_TOO_LARGE for rows of 2^31 scalars or more. */
 int64_t psig_logsig_backward_workspace(const PsigLogDesc *desc);
 
 /* grad_sig (rows, S) = adjoint of psig_logsig_forward applied to grad_logsig.
