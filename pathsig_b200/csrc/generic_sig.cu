@@ -436,10 +436,7 @@ __global__ void __launch_bounds__(kBlock) sig_backward_generic(const GenericPlan
 // private prefix copies are plain FMAs (as in the tiled kernels), which saves a fifth of the
 // instructions of a deep word.
 // ------------------------------------------------------------------------------------------
-#ifndef PSIG_LANE_WARPS
-#define PSIG_LANE_WARPS 16
-#endif
-constexpr int kLaneWarps = PSIG_LANE_WARPS;
+constexpr int kLaneWarps = 16;
 constexpr int kLaneBlock = 32 * kLaneWarps;
 constexpr int kLaneShallow = 6;  // depths up to this run an instance with per-thread arrays of this size
 

@@ -23,10 +23,7 @@
 namespace psig {
 namespace {
 
-#ifndef PSIG_HORNER_BLOCK
-#define PSIG_HORNER_BLOCK 256
-#endif
-constexpr int kHornerBlock = PSIG_HORNER_BLOCK;
+constexpr int kHornerBlock = 256;
 // Resident blocks per SM the forward kernel is compiled for.  A row is a chain of short phases with a
 // barrier each, so rows in flight per SM matter more than registers per thread (measured: 6 blocks
 // against 2 cut the forward time by 40 %); the values below are the largest that do not spill.
@@ -34,9 +31,6 @@ template <typename T, int NMAX> constexpr int forward_blocks_per_sm()
 {
     return sizeof(T) == 4 ? (NMAX <= 4 ? 8 : NMAX <= 8 ? 6 : 4) : 4;
 }
-#ifndef PSIG_HORNER_MINB_BWD
-#define PSIG_HORNER_MINB_BWD 1
-#endif
 constexpr size_t kHornerMaxSmem = 160 * 1024;
 // Balance of the backward gathers: a word whose sum has at least kTeamTerms terms gets a warp (lanes stride the
 // sum), shorter sums get a thread; sums over the first factor are cut into pieces of kPieceTerms terms.  With a
@@ -410,7 +404,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
 }
 
 template <typename T, int NMAX>
-__global__ void __launch_bounds__(kHornerBlock, PSIG_HORNER_MINB_BWD) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig, T *scratch)
 {
