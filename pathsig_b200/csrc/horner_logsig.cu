@@ -256,7 +256,9 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
     return cur;
 }
 
-template <typename T, int NMAX>
+// STREAMED is a compile-time switch so that the shared-memory instance keeps pointers the compiler knows
+// to be shared memory (generic addressing cost it 11-13 %).
+template <typename T, int NMAX, bool STREAMED>
 __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                       T *__restrict__ logsig, T *scratch)
 {
@@ -269,11 +271,13 @@ __global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
         T *l = logsig + row * p.out_width;
-        const T *xs = scratch ? s : xs_copy;
-        T *ta = scratch ? scratch + row * 2 * (long long)p.lower : xs_copy + p.lower;
+        const T *xs;
+        T *ta;
+        if constexpr (STREAMED) { xs = s; ta = scratch + row * 2 * (long long)p.lower; }
+        else { xs = xs_copy; ta = xs_copy + p.lower; }
         T *tb = ta + p.lower;
         __syncthreads();  // the previous row's readers are done with the buffers
-        if (!scratch)
+        if constexpr (!STREAMED)
             for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) xs_copy[i] = s[i];
         __syncthreads();
         const T *t1 = build_t<T, NMAX>(p, xs, ta, tb, nullptr);
@@ -403,7 +407,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
     }
 }
 
-template <typename T, int NMAX>
+template <typename T, int NMAX, bool STREAMED>
 __global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig, T *scratch)
@@ -416,8 +420,10 @@ __global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const Hor
     const int N = p.depth;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T *s = sig + row * p.width;
-        const T *xs = scratch ? s : xs_copy;
-        T *gl = scratch ? scratch + row * (4 * (long long)p.lower + p.t_total) : xs_copy + p.lower;  // incoming gradient, degrees below N
+        const T *xs;
+        T *gl;                                     // incoming gradient, degrees below N
+        if constexpr (STREAMED) { xs = s; gl = scratch + row * (4 * (long long)p.lower + p.t_total); }
+        else { xs = xs_copy; gl = xs_copy + p.lower; }
         T *gx = gl + p.lower;                      // gradient wrt x, degrees below N
         T *ga = gx + p.lower;                      // adjoint of T_k
         T *gb = ga + p.lower;                      // adjoint of T_{k+1}
@@ -429,7 +435,7 @@ __global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const Hor
         T *out = gsig + row * p.width;
         __syncthreads();
         for (unsigned i = threadIdx.x; i < p.lower; i += blockDim.x) {
-            if (!scratch) xs_copy[i] = s[i];
+            if constexpr (!STREAMED) xs_copy[i] = s[i];
             const T gi = p.low_cols != nullptr ? T(0) : g[i];
             gl[i] = gi;
             gx[i] = gi;   // log S = x * 1 + ...: the degree-0 term of T_1 is 1
@@ -662,10 +668,16 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
         kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, logsig, scratch);
         return check_launch();
     };
-    if (p.depth <= 4) return launch(logsig_forward_horner<T, 4>);
-    if (p.depth <= 6) return launch(logsig_forward_horner<T, 6>);
-    if (p.depth <= 8) return launch(logsig_forward_horner<T, 8>);
-    return launch(logsig_forward_horner<T, 12>);
+    if (scratch) {
+        if (p.depth <= 4) return launch(logsig_forward_horner<T, 4, true>);
+        if (p.depth <= 6) return launch(logsig_forward_horner<T, 6, true>);
+        if (p.depth <= 8) return launch(logsig_forward_horner<T, 8, true>);
+        return launch(logsig_forward_horner<T, 12, true>);
+    }
+    if (p.depth <= 4) return launch(logsig_forward_horner<T, 4, false>);
+    if (p.depth <= 6) return launch(logsig_forward_horner<T, 6, false>);
+    if (p.depth <= 8) return launch(logsig_forward_horner<T, 8, false>);
+    return launch(logsig_forward_horner<T, 12, false>);
 }
 
 template <typename T>
@@ -685,10 +697,16 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
         kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, grad_logsig, grad_sig, scratch);
         return check_launch();
     };
-    if (p.depth <= 4) return launch(logsig_backward_horner<T, 4>);
-    if (p.depth <= 6) return launch(logsig_backward_horner<T, 6>);
-    if (p.depth <= 8) return launch(logsig_backward_horner<T, 8>);
-    return launch(logsig_backward_horner<T, 12>);
+    if (scratch) {
+        if (p.depth <= 4) return launch(logsig_backward_horner<T, 4, true>);
+        if (p.depth <= 6) return launch(logsig_backward_horner<T, 6, true>);
+        if (p.depth <= 8) return launch(logsig_backward_horner<T, 8, true>);
+        return launch(logsig_backward_horner<T, 12, true>);
+    }
+    if (p.depth <= 4) return launch(logsig_backward_horner<T, 4, false>);
+    if (p.depth <= 6) return launch(logsig_backward_horner<T, 6, false>);
+    if (p.depth <= 8) return launch(logsig_backward_horner<T, 8, false>);
+    return launch(logsig_backward_horner<T, 12, false>);
 }
 
 template int horner_logsig_backward<float>(const PsigLogDesc &, const LevelTable &, const float *, const float *,
