@@ -24,6 +24,8 @@ namespace psig {
 namespace {
 
 constexpr int kHornerBlock = 256;
+// The streamed form may run a row on a wider block when there are fewer rows than SMs can take.
+constexpr int kStreamedMaxBlock = 1024;
 // Resident blocks per SM the forward kernel is compiled for.  A row is a chain of short phases with a
 // barrier each, so rows in flight per SM matter more than registers per thread (measured: 6 blocks
 // against 2 cut the forward time by 40 %); the values below are the largest that do not spill.
@@ -259,7 +261,7 @@ __device__ __forceinline__ T *build_t(const HornerPlan &p, const T *xs, T *ta, T
 // STREAMED is a compile-time switch so that the shared-memory instance keeps pointers the compiler knows
 // to be shared memory (generic addressing cost it 11-13 %).
 template <typename T, int NMAX, bool STREAMED>
-__global__ void __launch_bounds__(kHornerBlock, forward_blocks_per_sm<T, NMAX>()) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(STREAMED ? kStreamedMaxBlock : kHornerBlock, STREAMED ? 1 : forward_blocks_per_sm<T, NMAX>()) logsig_forward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                       T *__restrict__ logsig, T *scratch)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -408,7 +410,7 @@ __device__ __forceinline__ void adjoint_in_smem(const HornerPlan &p, int M, cons
 }
 
 template <typename T, int NMAX, bool STREAMED>
-__global__ void __launch_bounds__(kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
+__global__ void __launch_bounds__(STREAMED ? kStreamedMaxBlock : kHornerBlock) logsig_backward_horner(const HornerPlan p, const T *__restrict__ sig,
                                                                        const T *__restrict__ glog,
                                                                        T *__restrict__ gsig, T *scratch)
 {
@@ -619,7 +621,14 @@ template <typename T> size_t backward_smem(const HornerPlan &p)
 // measured (config 4 and a dense (8,4) row): 128 threads gain 15 % forward and lose 35 % backward, 64 and
 // 32 threads lose up to 3.5x -- a row's phases are parallel inside the row, and rows in flight are limited
 // by shared memory, not by threads.
-unsigned horner_block(long long) { return kHornerBlock; }
+unsigned horner_block(long long rows, bool streamed)
+{
+    if (!streamed) return kHornerBlock;
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    // few large rows: a row is all the parallelism a block has
+    return rows < 2LL * sms ? kStreamedMaxBlock : rows < 16LL * sms ? 512u : (unsigned)kHornerBlock;
+}
 
 unsigned row_grid(long long rows) { return (unsigned)(rows < (1 << 20) ? rows : (1 << 20)); }
 
@@ -665,7 +674,7 @@ int horner_logsig_forward(const PsigLogDesc &desc, const LevelTable &lt, const T
     auto launch = [&](auto kernel) {
         // rows in flight are limited by shared memory under the default L1 split
         if (smem > 0 && !prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, logsig, scratch);
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows, scratch != nullptr), smem, stream>>>(p, sig, logsig, scratch);
         return check_launch();
     };
     if (scratch) {
@@ -694,7 +703,7 @@ int horner_logsig_backward(const PsigLogDesc &desc, const LevelTable &lt, const 
     const size_t smem = scratch ? 0 : backward_smem<T>(p);
     auto launch = [&](auto kernel) {
         if (smem > 0 && !prepare_kernel(kernel, smem, true)) return (int)PSIG_ERR_CUDA;
-        kernel<<<row_grid(desc.rows), horner_block(desc.rows), smem, stream>>>(p, sig, grad_logsig, grad_sig, scratch);
+        kernel<<<row_grid(desc.rows), horner_block(desc.rows, scratch != nullptr), smem, stream>>>(p, sig, grad_logsig, grad_sig, scratch);
         return check_launch();
     };
     if (scratch) {
