@@ -236,6 +236,19 @@ class Workload:
             events[1].record()
         return out.detach(), x.grad
 
+    def step_through(self):
+        """How step_fwd_bwd reaches the kernels (kernels_per_step counts this library's launches only)."""
+        import pathsig_b200 as ps
+        m = self.mod
+        if isinstance(m, ps.Signature) and not m.alternative_projection:
+            return "the two operators called directly"
+        if isinstance(m, ps.Signature):
+            closed = m._closure_pays(self.x)
+            return ("module + autograd" + ("; evaluated on the prefix closure of the word set, the requested columns "
+                    "selected by one torch gather forward and a zero-fill + scatter backward (3 torch kernels, "
+                    "not in kernels_per_step)" if closed else ""))
+        return "module + autograd"
+
     def kernels_per_step(self):
         """Kernels of this library launched by one forward + backward step (counted, not assumed)."""
         from pathsig_b200 import _load
@@ -584,6 +597,7 @@ def measure_workload(name, steps, warmup, world, device, per_rank_B=None, with_e
         "tflops_fwd_bwd": wl.flop_fwd_bwd() * world / (fb_med * 1e-3) / 1e12,
         "hbm_gbs_fwd_bwd": wl.bytes_fwd_bwd * world / (fb_med * 1e-3) / 1e9,
         "kernels_per_step": wl.kernels_per_step(),
+        "step_through": wl.step_through(),
     })
     if wl.units < 200000:
         # launch-bound workload: the same forward+backward step captured in a CUDA graph and
