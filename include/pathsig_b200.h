@@ -67,6 +67,13 @@ typedef enum PsigAlgo {
     PSIG_ALGO_CLOSURE = 3  /* prefix-closure kernels specialised for the word set, or PSIG_ERR_UNSUPPORTED */
 } PsigAlgo;
 
+/* PsigSigDesc.flags.  DETERMINISTIC: psig_sig_backward avoids floating-point atomics where a fixed-order
+ * alternative exists -- today the register-tiled kernels on un-windowed paths whose unit spans several
+ * blocks (d = 16): every block stores its share of the path gradient into its own slab of the workspace
+ * and a second kernel sums the slabs in a fixed order (psig_sig_backward_workspace grows accordingly).
+ * psig_sig_backward_reproducible tells whether the call selected by a description is bit-reproducible. */
+#define PSIG_FLAG_DETERMINISTIC 1
+
 /* Problem description shared by the signature entry points. */
 typedef struct PsigSigDesc {
     int32_t dtype;                            /* PsigDtype */
@@ -80,7 +87,7 @@ typedef struct PsigSigDesc {
     const int64_t *words;                     /* device codes of non-complete degrees, or NULL */
     int64_t level_sizes[PSIG_MAX_DEPTH + 1];  /* host */
     int32_t algo;                             /* PsigAlgo */
-    int32_t reserved;
+    int32_t flags;                            /* PSIG_FLAG_* bits, 0 by default */
     const int64_t *words_host;                /* optional HOST copy of `words` (same layout).  The prefix-closure
                                                  kernels are generated from the word set, which has to be readable
                                                  on the host; NULL rules that family out for projected rows. */
@@ -157,6 +164,11 @@ int64_t psig_sig_backward_workspace(const PsigSigDesc *desc);
  * Replaces pathsig::signature_backward (src/pathsig/backward/sig_backward_launch.cu:83-303). */
 int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
                       void *grad_path, void *workspace, int64_t workspace_bytes, void *stream);
+/* Host only, no counterpart in the reference (whose backward always adds with float atomics,
+ * src/pathsig/backward/sig_backward_kernels.cu:317): 1 when psig_sig_backward gives the same bits on every
+ * run for this description (register-tiled kernels, no windows, and either one block per unit or
+ * PSIG_FLAG_DETERMINISTIC), 0 when some sums are float atomics, negative PsigStatus on a bad description. */
+int psig_sig_backward_reproducible(const PsigSigDesc *desc);
 
 /* Scalars per row of the cache argument of psig_logsig_forward / psig_logsig_backward: 0 when the row
  * fits the row-in-shared-memory form of the kernels; S*depth -- the shape of the reference's table of

@@ -21,6 +21,7 @@ ABI_VERSION = 2
 
 PSIG_F32, PSIG_F64 = 0, 1
 ALGO_AUTO, ALGO_GENERIC, ALGO_TILED, ALGO_CLOSURE = 0, 1, 2, 3
+FLAG_DETERMINISTIC = 1   # PSIG_FLAG_DETERMINISTIC of include/pathsig_b200.h
 
 _lock = threading.Lock()
 _lib = None
@@ -41,7 +42,7 @@ class SigDesc(ctypes.Structure):
         ("words", ctypes.c_void_p),
         ("level_sizes", ctypes.c_int64 * (MAX_DEPTH + 1)),
         ("algo", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
         ("words_host", ctypes.c_void_p),
     ]
 
@@ -84,6 +85,7 @@ EXPORTS = {
     "psig_sig_forward": (_int, [_SigP, _vp, _vp, _vp]),
     "psig_sig_backward_workspace": (_i64, [_SigP]),
     "psig_sig_backward": (_int, [_SigP, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "psig_sig_backward_reproducible": (_int, [_SigP]),
     "psig_logsig_cache_size": (_i64, [_LogP]),
     "psig_logsig_forward": (_int, [_LogP, _vp, _vp, _vp, _vp]),
     "psig_logsig_backward_workspace": (_i64, [_LogP]),

@@ -251,6 +251,16 @@ int64_t psig_sig_backward_workspace(const PsigSigDesc *desc)
     return (int64_t)dtype_size(desc->dtype) * desc->B * (desc->L - 1) * desc->d;
 }
 
+int psig_sig_backward_reproducible(const PsigSigDesc *desc)
+{
+    LevelTable lt;
+    int rc = sig_table(desc, &lt);
+    if (rc != PSIG_OK) return rc;
+    const Family family = select_family(desc, lt, &rc);
+    if (rc != PSIG_OK) return rc;
+    return family == Family::kTiled && tiled_sig_backward_reproducible(*desc) ? 1 : 0;
+}
+
 int psig_sig_backward(const PsigSigDesc *desc, const void *path, const void *sig, const void *grad_sig,
                       void *grad_path, void *workspace, int64_t workspace_bytes, void *stream)
 {

@@ -69,6 +69,7 @@ bool tiled_supported(const PsigSigDesc &desc);
 template <typename T>
 int tiled_sig_forward(const PsigSigDesc &desc, const T *path, T *out, cudaStream_t stream);
 int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc);
+bool tiled_sig_backward_reproducible(const PsigSigDesc &desc);
 // Bounded wait of the bulk-copy staging: poll limit (test hook) and read-and-clear count of waits that ran out.
 int tiled_set_bulk_wait_polls(int polls);
 long long tiled_bulk_copy_timeouts();

@@ -29,6 +29,7 @@
 // float32 only) and dispatches on the dtype of the description.
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstdint>
 #include <type_traits>
 
@@ -63,7 +64,17 @@ bool tiled_supported(const PsigSigDesc &desc)
     return desc.dtype == PSIG_F32 ? f32::tiled_supported(desc) : f64::tiled_supported(desc);
 }
 
-int64_t tiled_sig_backward_workspace(const PsigSigDesc &) { return 0; }
+int64_t tiled_sig_backward_workspace(const PsigSigDesc &desc)
+{
+    return desc.dtype == PSIG_F32 ? f32::backward_scratch_bytes(desc, nullptr) : f64::backward_scratch_bytes(desc, nullptr);
+}
+
+bool tiled_sig_backward_reproducible(const PsigSigDesc &desc)
+{
+    bool repro = false;
+    if (desc.dtype == PSIG_F32) f32::backward_scratch_bytes(desc, &repro); else f64::backward_scratch_bytes(desc, &repro);
+    return repro;
+}
 
 int tiled_top_plan(const PsigSigDesc &desc, bool backward, unsigned char *items, int *active)
 {

@@ -11,6 +11,7 @@
 // for memory, streams and dispatch only; fake (meta) implementations and autograd formulas are registered
 // from Python (pathsig_b200/ops.py).
 #include <ATen/ATen.h>
+#include <ATen/Context.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGraphsC10Utils.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -129,6 +130,8 @@ PsigSigDesc sig_desc(const at::Tensor &path, int64_t depth, bool alt, const at::
     desc.L = path.size(1);
     desc.projected = alt ? 1 : 0;
     desc.algo = g_algo.load();
+    // torch.use_deterministic_algorithms(True): ask for the fixed-order backward where the library has one
+    if (at::globalContext().deterministicAlgorithms()) desc.flags |= PSIG_FLAG_DETERMINISTIC;
     if (alt) {
         check_words(encoded_words);
         same_device(path, encoded_words, "encoded_words");

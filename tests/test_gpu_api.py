@@ -403,3 +403,49 @@ def test_run_to_run_reproducibility(ps, algo):
         assert torch.equal(a, b)
     finally:
         ps.ops.set_algorithm("auto")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_deterministic_mode_gives_a_bit_reproducible_backward_at_16_channels(ps, dtype):
+    """At d = 16, depth 4 a path spans 16 blocks of the reverse sweep, which by default add their shares of
+    the path gradient with float atomics (run-dependent last bits).  Under
+    ``torch.use_deterministic_algorithms(True)`` every block stores into its own slab of the workspace and
+    the slabs are summed in a fixed order: same bits on every run, same values as the default path within
+    the tolerance; the library reports which of the two it will run."""
+    import ctypes
+
+    from pathsig_b200 import _load
+    lib = _load.ensure_loaded()
+    x = util.brownian_path(6, 50, 16, seed=3, dtype=dtype).to(DEV)
+    mod = ps.Signature(depth=4)
+
+    def grads(n):
+        out = []
+        for _ in range(n):
+            xr = x.clone().requires_grad_(True)
+            y = mod(xr)
+            g = util.normal_like(y.shape, 7, dtype).to(DEV)
+            y.backward(g)
+            out.append(xr.grad.clone())
+        return out
+
+    default = grads(1)[0]
+    was = torch.are_deterministic_algorithms_enabled()
+    torch.use_deterministic_algorithms(True)
+    try:
+        fixed = grads(4)
+    finally:
+        torch.use_deterministic_algorithms(was)
+    assert all(torch.equal(fixed[0], g) for g in fixed[1:])
+    assert util.rel_error(fixed[0], default) < util.TOL[dtype]
+    desc = _load.SigDesc()
+    desc.dtype = _load.PSIG_F32 if dtype == torch.float32 else _load.PSIG_F64
+    desc.B, desc.L, desc.d, desc.depth = 6, 50, 16, 4
+    assert lib.psig_sig_backward_reproducible(ctypes.byref(desc)) == 0
+    assert lib.psig_sig_backward_workspace(ctypes.byref(desc)) == 0
+    desc.flags = _load.FLAG_DETERMINISTIC
+    assert lib.psig_sig_backward_reproducible(ctypes.byref(desc)) == 1
+    blocks_per_path = 16 if dtype == torch.float32 else 32   # the float64 instance owns half as many first letters per thread
+    assert lib.psig_sig_backward_workspace(ctypes.byref(desc)) == x.element_size() * 6 * blocks_per_path * 50 * 16
+    desc.d, desc.flags = 8, 0                      # one block per unit: reproducible without the flag
+    assert lib.psig_sig_backward_reproducible(ctypes.byref(desc)) == 1
